@@ -1,0 +1,210 @@
+"""TEST INFRASTRUCTURE ONLY -- the CPU checker for the CUDA library.
+
+``oracle.port``   : ctypes handle on ``libbolt_oracle.so`` (scalar C restatement of the
+                    reference arithmetic, ``bolt_oracle.c``); builds it with gcc on first use.
+``oracle.ref``    : ctypes handle on ``_ref/libbolt_ref.so`` (the reference's own x86
+                    AVX512-VNNI sources compiled with ``ref_shim.cpp``) or ``None`` when
+                    the library is absent or the host CPU lacks avx512_vnni.
+
+Only ``tests/``, ``__graft_entry__.smoke()`` and the CPU-baseline / reference legs of
+``bench.py`` may import this package.  The product package ``bolt_b200`` never does.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_c = ctypes
+_u32, _i32, _f32p = _c.c_uint32, _c.c_int, _c.POINTER(_c.c_float)
+_vp, _u64 = _c.c_void_p, _c.c_uint64
+
+
+def build_port():
+    """Compile the scalar restatement (a second or two of gcc)."""
+    subprocess.check_call(["make", "-s", "-C", _HERE, "all"])
+
+
+def build_ref(bolt_root="/root/reference"):
+    """Compile the reference's own int8 sources from the mounted tree, if it is there."""
+    if not os.path.isdir(bolt_root):
+        return False
+    subprocess.check_call(["make", "-s", "-C", _HERE, "ref", "BOLT_ROOT=" + bolt_root])
+    return True
+
+
+def host_has_avx512_vnni():
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.startswith("flags"):
+                    return "avx512_vnni" in line.split()
+    except OSError:
+        pass
+    return False
+
+
+def ptr(a):
+    """Raw pointer of a numpy array (or None)."""
+    if a is None:
+        return None
+    assert a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data_as(_vp)
+
+
+class ConvShape(_c.Structure):
+    _fields_ = [(k, _u32) for k in (
+        "n", "ic", "ih", "iw", "oc", "fh", "fw", "stride_h", "stride_w", "pad_t", "pad_b",
+        "pad_l", "pad_r", "dil_h", "dil_w", "cin_block", "cout_block", "relu", "out_u8")]
+
+
+class BnnShape(_c.Structure):
+    _fields_ = [(k, _u32) for k in (
+        "n", "ic", "ih", "iw", "oc", "fh", "fw", "stride_h", "stride_w", "pad_t", "pad_b",
+        "pad_l", "pad_r", "xnor")]
+
+
+def _load_port():
+    so = os.path.join(_HERE, "libbolt_oracle.so")
+    src = os.path.join(_HERE, "bolt_oracle.c")
+    if not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
+        build_port()
+    lib = _c.CDLL(so)
+    lib.oracle_cvt_rne.restype = _c.c_int32
+    lib.oracle_cvt_rne.argtypes = [_c.c_float]
+    lib.oracle_usat8.restype = _c.c_uint8
+    lib.oracle_usat8.argtypes = [_c.c_int32]
+    lib.oracle_offsetc.argtypes = [_vp, _u32, _u32, _i32, _vp]
+    lib.oracle_gemm_u8s8.argtypes = [_u32, _u32, _u32, _vp, _i32, _vp, _i32, _vp, _vp, _vp]
+    lib.oracle_gemv_s8u8.argtypes = [_u32, _u32, _vp, _i32, _vp, _vp, _vp, _vp]
+    lib.oracle_scale_f32.restype = _c.c_float
+    lib.oracle_scale_f32.argtypes = [_vp, _u64]
+    lib.oracle_scale_i32.restype = _c.c_float
+    lib.oracle_scale_i32.argtypes = [_vp, _u64]
+    lib.oracle_quantize_f32_u8.argtypes = [_vp, _u64, _vp, _vp, _i32]
+    lib.oracle_quantize_f32_i8.argtypes = [_vp, _u64, _vp, _vp, _i32]
+    lib.oracle_quantize_i32_u8.argtypes = [_vp, _u64, _vp, _vp]
+    lib.oracle_quantize_i32_i8.argtypes = [_vp, _u64, _vp, _vp]
+    lib.oracle_u8_to_i8.argtypes = [_vp, _u64, _vp]
+    lib.oracle_bias_offsetc.argtypes = [_vp, _vp, _u32, _c.c_float, _vp]
+    lib.oracle_dequantize_i32_f32.argtypes = [_vp, _u64, _c.c_float, _vp]
+    lib.oracle_dequantize_u8_f32.argtypes = [_vp, _u64, _c.c_float, _vp]
+    if hasattr(lib, "oracle_conv_int8"):
+        lib.oracle_conv_out_hw.argtypes = [_c.POINTER(ConvShape), _vp, _vp]
+        lib.oracle_conv_int8.argtypes = [_c.POINTER(ConvShape), _vp, _vp, _vp, _vp, _vp, _vp, _vp]
+    if hasattr(lib, "oracle_bnn_conv"):
+        lib.oracle_bnn_conv.argtypes = [_c.POINTER(BnnShape), _vp, _vp, _vp, _vp, _vp, _vp]
+        lib.oracle_f32_to_f16.restype = _c.c_uint16
+        lib.oracle_f32_to_f16.argtypes = [_c.c_float]
+        lib.oracle_f16_to_f32.restype = _c.c_float
+        lib.oracle_f16_to_f32.argtypes = [_c.c_uint16]
+        lib.oracle_f16_fma.restype = _c.c_uint16
+        lib.oracle_f16_fma.argtypes = [_c.c_uint16] * 3
+        lib.oracle_i32_to_f16.restype = _c.c_uint16
+        lib.oracle_i32_to_f16.argtypes = [_c.c_int32]
+    return lib
+
+
+def _load_ref():
+    so = os.path.join(_HERE, "_ref", "libbolt_ref.so")
+    if not os.path.exists(so) or not host_has_avx512_vnni():
+        return None
+    lib = _c.CDLL(so)
+    lib.ref_set_threads.argtypes = [_i32]
+    lib.ref_get_threads.restype = _i32
+    lib.ref_gemm_plan.restype = _vp
+    lib.ref_gemm_plan.argtypes = [_u32, _u32, _u32, _i32, _i32, _vp, _i32]
+    lib.ref_gemm_run.argtypes = [_vp, _vp, _vp, _vp, _vp]
+    lib.ref_gemm_offsetc.argtypes = [_vp, _vp]
+    lib.ref_gemm_free.argtypes = [_vp]
+    lib.ref_gemm_unpacked.argtypes = [_u32, _u32, _u32, _i32, _i32, _vp, _vp, _vp, _i32, _vp]
+    lib.ref_gemv_plan.restype = _vp
+    lib.ref_gemv_plan.argtypes = [_u32, _u32, _i32, _vp, _i32]
+    lib.ref_gemv_run.argtypes = [_vp, _vp, _vp, _vp, _vp]
+    lib.ref_gemv_free.argtypes = [_vp]
+    lib.ref_quantize.argtypes = [_u32, _i32, _vp, _i32, _vp, _vp, _i32]
+    lib.ref_dequantize.argtypes = [_u32, _i32, _vp, _vp, _vp]
+    lib.ref_bias_offsetc.argtypes = [_u32, _vp, _vp, _c.c_float, _vp]
+    lib.ref_conv_plan.restype = _vp
+    lib.ref_conv_plan.argtypes = [_u32] * 9 + [_i32] * 4 + [_vp]
+    lib.ref_conv_run.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp]
+    lib.ref_conv_free.argtypes = [_vp]
+    return lib
+
+
+port = _load_port()
+ref = _load_ref()
+
+DT_I8, DT_I32, DT_F32, DT_U8_Q = 1, 3, 6, 10
+_OUT_DT = {0: np.int32, 1: np.float32, 2: np.uint8}
+
+
+# ---- convenience wrappers used by the tests (numpy in, numpy out) -----------------------
+def _scale_arr(scale):
+    return None if scale is None else np.ascontiguousarray(np.asarray(scale, dtype=np.float32))
+
+
+def out_kind(scale):
+    if scale is None:
+        return 0
+    return 2 if scale[0] < 0 else 1
+
+
+def port_gemm(A, B, offsetC, scale=None, C_in=None, a_t=False, b_t=False):
+    """A u8 [M,K] (or [K,M] if a_t), B s8 [K,N] (or [N,K] if b_t)."""
+    M, K = (A.shape[1], A.shape[0]) if a_t else A.shape
+    N = B.shape[0] if b_t else B.shape[1]
+    kind = out_kind(scale)
+    C = np.zeros((M, N), _OUT_DT[kind]) if C_in is None else C_in.copy()
+    s = _scale_arr(scale)
+    port.oracle_gemm_u8s8(M, N, K, ptr(A), int(a_t), ptr(B), int(b_t), ptr(offsetC), ptr(C), ptr(s))
+    return C
+
+
+def port_offsetc(B, b_t=False):
+    N, K = B.shape if b_t else B.shape[::-1]
+    out = np.zeros(N, np.int32)
+    port.oracle_offsetc(ptr(B), K, N, int(b_t), ptr(out))
+    return out
+
+
+def port_gemv(W, x, offsetC, scale=None, y_in=None, w_t=False):
+    N, K = W.shape[::-1] if w_t else W.shape
+    kind = out_kind(scale)
+    y = np.zeros(N, _OUT_DT[kind]) if y_in is None else y_in.copy()
+    s = _scale_arr(scale)
+    port.oracle_gemv_s8u8(N, K, ptr(W), int(w_t), ptr(x), ptr(offsetC), ptr(y), ptr(s))
+    return y
+
+
+def ref_gemm(A, B, scale=None, C_in=None, a_t=False, b_t=False, offsetC=None, prepack=True):
+    M, K = (A.shape[1], A.shape[0]) if a_t else A.shape
+    N = B.shape[0] if b_t else B.shape[1]
+    kind = out_kind(scale)
+    C = np.zeros((M, N), _OUT_DT[kind]) if C_in is None else C_in.copy()
+    s = _scale_arr(scale)
+    if not prepack:
+        assert offsetC is None
+        rc = ref.ref_gemm_unpacked(M, N, K, int(a_t), int(b_t), ptr(A), ptr(B), ptr(C), kind, ptr(s))
+        assert rc == 0
+        return C
+    pl = ref.ref_gemm_plan(M, N, K, int(a_t), int(b_t), ptr(B), kind)
+    assert pl
+    rc = ref.ref_gemm_run(pl, ptr(A), ptr(C), ptr(s), ptr(offsetC))
+    ref.ref_gemm_free(pl)
+    assert rc == 0
+    return C
+
+
+def ref_gemv(W, x, scale=None, y_in=None, w_t=False, offsetC=None):
+    N, K = W.shape[::-1] if w_t else W.shape
+    kind = out_kind(scale)
+    y = np.zeros(N, _OUT_DT[kind]) if y_in is None else y_in.copy()
+    s = _scale_arr(scale)
+    pl = ref.ref_gemv_plan(N, K, int(w_t), ptr(W), kind)
+    assert pl
+    rc = ref.ref_gemv_run(pl, ptr(x), ptr(y), ptr(s), ptr(offsetC))
+    ref.ref_gemv_free(pl)
+    assert rc == 0
+    return y
