@@ -1,0 +1,605 @@
+// gemm_i8_tcgen05.cu -- u8 x s8 -> s32 GEMM on the 5th-generation tensor cores of sm_100a.
+//
+//   C[M,N] = epilogue( offsetC[n] + sum_k A_u8[m,k] * B_s8[n,k] )        (both operands K-major)
+//
+// Replaces the AVX512-VNNI micro-kernels and their driver in Bolt
+// (compute/blas_enhance/src/cpu/x86/int8/avx512/mmm_avx512_vnni.cpp:383-1891).
+//
+// One persistent CTA per SM, 192 threads, three roles:
+//   warp 0      TMA producer: cp.async.bulk.tensor 2-D loads of a 128 x 128-byte A tile and a
+//               BLOCK_N x 128-byte B tile per pipeline stage, 128-byte swizzle, mbarrier complete_tx
+//   warp 1      MMA issuer: one thread issues tcgen05.mma.cta_group::1.kind::i8 (M=128, N=BLOCK_N,
+//               K=32 per instruction, A unsigned / B signed, int32 accumulate, no saturation) with
+//               shared-memory matrix descriptors; accumulators live in tensor memory (2 x 256 columns,
+//               so the epilogue of tile i overlaps the main loop of tile i+1)
+//   warps 2..5  epilogue: tcgen05.ld 32 lanes x 32 columns per warp, fused offsetC / C_in add and the
+//               reference's s32 -> f32 / u8 conversions, direct 16-byte global stores
+// Every mbarrier wait is bounded; a wait that runs out sets the device status word and the CTA
+// drains and exits (tensor memory is always released).
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 128;         // bytes of K per stage = one 128B swizzle row
+constexpr int MAX_BLOCK_N = 256;
+constexpr int STAGES = 4;
+constexpr int UMMA_K = 32;           // K per tcgen05.mma.kind::i8
+constexpr int NUM_THREADS = 192;
+constexpr int EPI_THREADS = 128;
+constexpr uint32_t TMEM_COLS = 512;  // 2 accumulators x 256 columns
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // per wait; far above any legitimate wait
+
+constexpr int SMEM_A_STAGE = BLOCK_M * BLOCK_K;        // 16 KiB
+constexpr int SMEM_B_STAGE = MAX_BLOCK_N * BLOCK_K;    // 32 KiB
+
+struct __align__(8) SmemCtl {
+    uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+    // per epilogue warp, double buffered by accumulator: column constants of the current tile
+    int32_t offs[4][2][MAX_BLOCK_N];
+    float colf[4][2][MAX_BLOCK_N];
+};
+
+constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * (SMEM_A_STAGE + SMEM_B_STAGE) +
+    sizeof(SmemCtl);
+
+struct Params {
+    uint32_t M, N, K;
+    uint32_t block_n;       // multiple of 32, <= 256
+    uint32_t tiles_m, tiles_n, num_kb;
+    void *C;
+    GemmEpilogue ep;
+    int *status;
+    int vec_ok;             // rows of C are 16-byte aligned -> vector stores allowed
+};
+
+// ---- PTX wrappers ----------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p)
+{
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the limit ran out (the caller then aborts the CTA's work).
+__device__ __forceinline__ uint64_t global_ns()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
+{
+    if (mbar_try_wait(bar, parity)) {
+        return true;
+    }
+    const uint64_t t0 = global_ns();
+    for (;;) {
+        for (int i = 0; i < 64; ++i) {
+            if (mbar_try_wait(bar, parity)) {
+                return true;
+            }
+        }
+        if (global_ns() - t0 > WAIT_LIMIT_NS) {
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(const CUtensorMap *map, uint64_t *bar, void *dst, int x, int y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before()
+{
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after()
+{
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_commit(uint64_t *bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+    uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+          "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+          "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+          "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait()
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows of 128 bytes, groups of
+// 8 rows 1024 bytes apart (stride byte offset), descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;             // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;   // stride byte offset
+    d |= (uint64_t)1 << 46;             // version
+    d |= (uint64_t)2 << 61;             // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor of kind::i8: D = s32 (2 << 4), A = u8 (0 << 7), B = s8 (1 << 10), both
+// K-major, N >> 3 at bit 17, M >> 4 at bit 24; dense, no saturation.
+__device__ __forceinline__ uint32_t make_idesc_i8(uint32_t n)
+{
+    return (2u << 4) | (0u << 7) | (1u << 10) | ((n >> 3) << 17) | ((uint32_t)(BLOCK_M >> 4) << 24);
+}
+
+// ---- epilogue for 32 consecutive columns of one row --------------------------------------------
+__device__ __forceinline__ void store_chunk(const Params &p, const int32_t *offs, const float *colf, uint32_t m,
+    uint32_t n0 /*global col of r[0]*/, uint32_t cl /*tile-local col of r[0]*/, uint32_t (&r)[32])
+{
+    const GemmEpilogue &ep = p.ep;
+    const uint32_t ncols = min(32u, p.N - n0);
+    const size_t row_off = (size_t)m * p.N + n0;
+    const bool full_vec = p.vec_ok && ncols == 32;
+    int acc[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        acc[j] = (int)r[j] + offs[cl + j];
+    }
+    if (ep.out_kind != 2 && ep.accumulate) {
+        const int32_t *cin = reinterpret_cast<const int32_t *>(p.C) + row_off;
+        if (full_vec) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                int4 v = *reinterpret_cast<const int4 *>(cin + j);
+                acc[j] += v.x;
+                acc[j + 1] += v.y;
+                acc[j + 2] += v.z;
+                acc[j + 3] += v.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if ((uint32_t)j < ncols) {
+                    acc[j] += cin[j];
+                }
+            }
+        }
+    }
+    if (ep.out_kind == 0) {
+        int32_t *out = reinterpret_cast<int32_t *>(p.C) + row_off;
+        if (full_vec) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                *reinterpret_cast<int4 *>(out + j) = make_int4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if ((uint32_t)j < ncols) {
+                    out[j] = acc[j];
+                }
+            }
+        }
+        return;
+    }
+    // conversion factor per element
+    float rs = 0.f;
+    const bool per_elem = ep.per_channel && ep.row_scale != nullptr;
+    if (per_elem) {
+        rs = ep.row_scale[m];
+    }
+    if (ep.out_kind == 1) {
+        float *out = reinterpret_cast<float *>(p.C) + row_off;
+        float f[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            float fac = colf[cl + j];
+            if (per_elem) {
+                fac = __fdiv_rn(ep.num, __fmul_rn(rs, fac));
+            }
+            f[j] = acc_to_f32(acc[j], fac);
+        }
+        if (full_vec) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                *reinterpret_cast<float4 *>(out + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if ((uint32_t)j < ncols) {
+                    out[j] = f[j];
+                }
+            }
+        }
+        return;
+    }
+    uint8_t *out = reinterpret_cast<uint8_t *>(p.C) + row_off;
+    uint32_t w[8];
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+        uint32_t b[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            float fac = colf[cl + j + t];
+            if (per_elem) {
+                fac = __fdiv_rn(ep.num, __fmul_rn(rs, fac));
+            }
+            b[t] = acc_to_u8(acc[j + t], fac);
+        }
+        w[j >> 2] = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+    }
+    if (full_vec) {
+        *reinterpret_cast<uint4 *>(out) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4 *>(out + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            if ((uint32_t)j < ncols) {
+                out[j] = (uint8_t)(w[j >> 2] >> (8 * (j & 3)));
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+    const Params p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    // 128-byte swizzled tiles need 1024-byte aligned bases
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *smem_a = smem;
+    uint8_t *smem_b = smem + STAGES * SMEM_A_STAGE;
+    SmemCtl *ctl = reinterpret_cast<SmemCtl *>(smem + STAGES * (SMEM_A_STAGE + SMEM_B_STAGE));
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t num_tiles = p.tiles_m * p.tiles_n;
+    const uint32_t stage_bytes = (uint32_t)(BLOCK_M + p.block_n) * BLOCK_K;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&ctl->full[s], 1);
+            mbar_init(&ctl->empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&ctl->tmem_full[a], 1);
+            mbar_init(&ctl->tmem_empty[a], EPI_THREADS);
+        }
+        ctl->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(&ctl->tmem_base)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = ctl->tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------- TMA producer -------------------------------------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+                const int m0 = (int)((tile % p.tiles_m) * BLOCK_M);
+                const int n0 = (int)((tile / p.tiles_m) * p.block_n);
+                for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
+                    if (!mbar_wait(&ctl->empty[stage], phase ^ 1)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(&ctl->full[stage], stage_bytes);
+                    tma_load_2d(&map_a, &ctl->full[stage], smem_a + stage * SMEM_A_STAGE, (int)(kb * BLOCK_K), m0);
+                    tma_load_2d(&map_b, &ctl->full[stage], smem_b + stage * SMEM_B_STAGE, (int)(kb * BLOCK_K), n0);
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+            if (!ok) {
+                atomicExch(p.status, 1);
+                atomicExch(&ctl->abort_flag, 1u);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------- MMA issuer ---------------------------------------------
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc_i8(p.block_n);
+            uint32_t stage = 0, phase = 0;
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++it) {
+                const uint32_t acc = it & 1;
+                const uint32_t acc_phase = (it >> 1) & 1;
+                if (!mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1)) {
+                    ok = false;
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * MAX_BLOCK_N;
+                for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
+                    if (!mbar_wait(&ctl->full[stage], phase)) {
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint64_t da = make_desc_sw128(smem_u32(smem_a + stage * SMEM_A_STAGE));
+                    const uint64_t db = make_desc_sw128(smem_u32(smem_b + stage * SMEM_B_STAGE));
+#pragma unroll
+                    for (uint32_t k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                        // advancing K inside the 128-byte swizzle row: +32 bytes = +2 in the
+                        // 16-byte units of the descriptor's start-address field
+                        umma_i8(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    tcgen05_commit(&ctl->empty[stage]);  // frees the stage once these MMAs retire
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (!ok) {
+                    break;
+                }
+                tcgen05_commit(&ctl->tmem_full[acc]);
+            }
+            if (!ok) {
+                atomicExch(p.status, 2);
+                atomicExch(&ctl->abort_flag, 1u);
+            }
+        }
+    } else {
+        // ------------------------------- epilogue warps 2..5 ------------------------------------
+        const uint32_t quad = warp & 3;  // tensor-memory lane quadrant this warp may read
+        const uint32_t ew = warp - 2;    // 0..3: which private copy of the column constants
+        const GemmEpilogue &ep = p.ep;
+        uint32_t it = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+            const uint32_t acc = it & 1;
+            const uint32_t acc_phase = (it >> 1) & 1;
+            const uint32_t m0 = (tile % p.tiles_m) * BLOCK_M;
+            const uint32_t n0 = (tile / p.tiles_m) * p.block_n;
+            // per-tile column constants -> this warp's shared-memory copy (double buffered by `acc`,
+            // so only a warp-level sync is needed)
+            int32_t *offs = ctl->offs[ew][acc];
+            float *colf = ctl->colf[ew][acc];
+            for (uint32_t j = lane; j < p.block_n; j += 32) {
+                const uint32_t n = n0 + j;
+                int32_t o = 0;
+                float f = ep.factor;
+                if (n < p.N) {
+                    if (ep.offsetC != nullptr) {
+                        o = ep.offsetC[n];
+                    }
+                    if (ep.per_channel) {
+                        const float sb = ep.col_scale ? ep.col_scale[n] : ep.sB;
+                        // with per-row scales the division is done per element; keep sB here
+                        const float sa = ep.sA_dev ? *ep.sA_dev : ep.sA;
+                        f = ep.row_scale ? sb : __fdiv_rn(ep.num, __fmul_rn(sa, sb));
+                    }
+                }
+                offs[j] = o;
+                colf[j] = f;
+            }
+            __syncwarp();
+            ok = mbar_wait(&ctl->tmem_full[acc], acc_phase);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                break;
+            }
+            tcgen05_fence_after();
+            const uint32_t m = m0 + quad * 32 + lane;
+            for (uint32_t c = 0; c < p.block_n; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((quad * 32u) << 16) + acc * MAX_BLOCK_N + c, r);
+                tmem_ld_wait();
+                if (m < p.M && n0 + c < p.N) {
+                    store_chunk(p, offs, colf, m, n0 + c, c, r);
+                }
+            }
+            tcgen05_fence_before();
+            mbar_arrive(&ctl->tmem_empty[acc]);
+        }
+        if (!ok && lane == 0) {
+            atomicExch(p.status, 3);
+            atomicExch(&ctl->abort_flag, 1u);
+        }
+    }
+
+    __syncthreads();
+    if (ctl->abort_flag != 0) {
+        // give copies that may still be in flight time to land before shared memory is released
+        for (int i = 0; i < 64; ++i) {
+            __nanosleep(2000);
+        }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+        }
+    });
+    return fn;
+}
+
+// 2-D byte tensor [rows][inner] with row pitch `pitch`, box = 128 bytes x box_rows, 128B swizzle,
+// out-of-range elements read as zero.
+bool make_map(CUtensorMap *map, const void *base, uint64_t inner, uint64_t rows, uint64_t pitch, uint32_t box_rows)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) {
+        return false;
+    }
+    cuuint64_t dims[2] = {inner, rows};
+    cuuint64_t strides[1] = {pitch};
+    cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+// Tile width: the widest of 256 / 192 / 128 / 64 / 32 columns that still gives every SM a tile,
+// preferring the one that wastes the least of the last wave.
+uint32_t pick_block_n(uint32_t M, uint32_t N, int sms)
+{
+    const uint32_t tiles_m = (M + BLOCK_M - 1) / BLOCK_M;
+    const uint32_t cand[] = {256, 224, 192, 160, 128, 96, 64, 32};
+    uint32_t best = 32;
+    double best_cost = 1e30;
+    for (uint32_t bn : cand) {
+        if (bn > B200_ALIGN(N, 32) && bn != 32) {
+            continue;
+        }
+        const uint32_t tiles = tiles_m * ((N + bn - 1) / bn);
+        const uint32_t waves = (tiles + sms - 1) / sms;
+        // time ~ waves x (tile cost); narrow tiles pay more shared-memory traffic per MAC
+        const double cost = (double)waves * (bn + 48.0);
+        if (cost < best_cost) {
+            best_cost = cost;
+            best = bn;
+        }
+    }
+    return best;
+}
+
+}  // namespace
+
+bool gemm_tcgen05_eligible(uint32_t M, uint32_t N, uint32_t K, const void *A, const void *B, uint32_t Kp,
+    bool a_transposed)
+{
+    if (a_transposed || M == 0 || N == 0 || K == 0) {
+        return false;
+    }
+    // TMA: 16-byte aligned bases and row pitches
+    if ((K % 16) != 0 || (Kp % 16) != 0) {
+        return false;
+    }
+    if ((reinterpret_cast<uintptr_t>(A) % 16) != 0 || (reinterpret_cast<uintptr_t>(B) % 16) != 0) {
+        return false;
+    }
+    return encode_fn() != nullptr;
+}
+
+EE launch_gemm_tcgen05(uint32_t M, uint32_t N, uint32_t K, const uint8_t *A, const int8_t *B, uint32_t Kp,
+    void *C, const GemmEpilogue &ep, cudaStream_t st)
+{
+    DeviceCtx *c = ctx();
+    if (c == nullptr) {
+        return UNKNOWN;
+    }
+    static std::once_flag attr_once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(attr_once, [] {
+        attr_err = cudaFuncSetAttribute(
+            gemm_u8s8_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    });
+    B200_CUDA(attr_err);
+
+    Params p;
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.block_n = pick_block_n(M, N, c->sm_count);
+    p.tiles_m = (M + BLOCK_M - 1) / BLOCK_M;
+    p.tiles_n = (N + p.block_n - 1) / p.block_n;
+    p.num_kb = (K + BLOCK_K - 1) / BLOCK_K;
+    p.C = C;
+    p.ep = ep;
+    p.status = c->d_status;
+    const size_t esz = ep.out_kind == 2 ? 1 : 4;
+    p.vec_ok = ((N * esz) % 16 == 0) && (reinterpret_cast<uintptr_t>(C) % 16 == 0);
+
+    CUtensorMap map_a, map_b;
+    if (!make_map(&map_a, A, K, M, K, BLOCK_M) ||
+        !make_map(&map_b, B, K, B200_ALIGN(N, 16), Kp, p.block_n)) {
+        return NOT_SUPPORTED;
+    }
+    const uint32_t tiles = p.tiles_m * p.tiles_n;
+    const uint32_t grid = tiles < (uint32_t)c->sm_count ? tiles : (uint32_t)c->sm_count;
+    gemm_u8s8_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
+    count_launch();
+    B200_CUDA(cudaGetLastError());
+    return SUCCESS;
+}
+
+}  // namespace b200
