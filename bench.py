@@ -1,0 +1,331 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized GEMM path on the BERT-base-shaped int8 linear stack.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+A step is one pass of 4096 tokens through 12 x (768 -> 3072 -> 768) quantized linear layers:
+dynamic per-tensor u8 quantization of the fp32 input, 24 u8 x s8 GEMMs with per-output-channel
+weight scales and fused requantization to u8 between layers, fp32 output.  Synthetic seeded data.
+
+`value`  : int8 GEMM TOP/s (2*M*N*K ops of the 24 GEMMs) with the input resident in HBM,
+           the whole step replayed as one CUDA graph, L2 flushed between timed steps.
+`e2e`    : the same metric through LinearStack.run_host: pinned host input -> H2D -> step -> D2H.
+`roofline`: the tcgen05 GEMM kernel alone (24 launches per pass) against 2 x the measured bf16 peak.
+`cpu_baseline` / --impl reference: the reference's own x86 AVX512-VNNI code (or the scalar oracle
+           port when that cannot run) on the host cores, same shapes, bounded sample.
+With N > 1 every rank runs its own 4096-token batch (weak scaling, no collective on the data path).
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M_TOKENS, LAYERS, HIDDEN, INTER = 4096, 12, 768, 3072
+OPS_PER_STEP = 2 * M_TOKENS * HIDDEN * INTER * 2 * LAYERS  # 463.86 GOP
+WORKLOAD = "bert_base_int8_linear_stack: 12 x (768->3072->768), M=4096 tokens, s8 per-channel weights, u8 per-tensor activations, fused requant, fp32 out"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of gemm_u8s8_tcgen05_kernel, averaged over
+# the 24 launches of one pass (profiles/gemm_u8s8_tcgen05_bert_stack.md); None until captured.
+GEMM_DRAM_TRAFFIC_PER_LAUNCH = None
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return json.load(f), "measured"
+    except (OSError, ValueError):
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.idx), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------ CPU arm
+def cpu_stack_baseline(seconds=12.0, threads=None):
+    """The reference's CPU path for the same stack: per layer an int8 GEMM through Bolt's
+    matrix_matrix_multiply (pre-packed weight, int32 out, OpenMP over all host threads -- the only
+    part of the path the reference threads, mmm_avx512_vnni.cpp:1858-1860) followed by its
+    I32 -> U8_Q requantization (quantize_x86, single thread as shipped)."""
+    import oracle as O
+    from bolt_b200 import synth
+    from bolt_b200.linear_stack import quantize_weight_host
+
+    cores = threads or os.cpu_count() or 1
+    if O.ref is not None:
+        kind, m = "reference", M_TOKENS
+        O.ref.ref_set_threads(cores)
+    else:
+        kind, m, cores = "port", 64, 1
+    shapes = [(HIDDEN, INTER), (INTER, HIDDEN)]
+    ws = [quantize_weight_host(synth.normal(100 + i, s, 0.02), False)[0] for i, s in enumerate(shapes)]
+    acts = [synth.u8(7, (m, HIDDEN)), synth.u8(8, (m, INTER))]
+    if kind == "reference":
+        plans = [O.ref.ref_gemm_plan(m, n, k, 0, 0, O.ptr(w), 0) for (k, n), w in zip(shapes, ws)]
+        accs = [np.zeros((m, n), np.int32) for (_, n) in shapes]
+        qs = [np.zeros(m * n, np.uint8) for (_, n) in shapes]
+
+        def layer_pair():
+            for j in range(2):
+                accs[j][...] = 0
+                O.ref.ref_gemm_run(plans[j], O.ptr(acts[j]), O.ptr(accs[j]), None, None)
+                sc = np.array([0.5, 300.0], np.float32)
+                O.ref.ref_quantize(accs[j].size, O.DT_I32, O.ptr(accs[j]), O.DT_U8_Q, O.ptr(qs[j]), O.ptr(sc), 0)
+    else:
+        offs = [O.port_offsetc(w) for w in ws]
+
+        def layer_pair():
+            for j in range(2):
+                O.port_gemm(acts[j], ws[j], offs[j], [-1, 0.002])
+
+    layer_pair()  # warm-up
+    t0 = time.perf_counter()
+    pairs = 0
+    while True:
+        layer_pair()
+        pairs += 1
+        el = time.perf_counter() - t0
+        if el > seconds or (kind == "reference" and pairs >= 10 * LAYERS):
+            break
+    if kind == "reference":
+        for p in plans:
+            O.ref.ref_gemm_free(p)
+    ops = pairs * 2 * m * HIDDEN * INTER * 2
+    tops = ops / el / 1e12
+    sample = "%d layer pairs (768->3072->768) at M=%d, %s, %.1f s" % (
+        pairs, m, "Bolt x86 AVX512-VNNI GEMM (OpenMP) + single-thread requantize" if kind == "reference"
+        else "scalar oracle port (host CPU lacks avx512_vnni or the reference build is absent)", el)
+    return {"value": tops, "unit": "TOP/s", "cores": cores, "kind": kind, "sample": sample}, el / pairs * LAYERS
+
+
+def run_reference_arm(args, rank):
+    if rank != 0:
+        return
+    base, step_s = cpu_stack_baseline(seconds=max(5.0, min(60.0, 4.0 * (args.steps + args.warmup))))
+    line = {
+        "impl": "reference", "metric": "int8_gemm_tops", "value": base["value"], "unit": "TOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8*s8->s32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "l2": "host CPU run"},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": "TOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------ GPU arm
+def run_b200_arm(args, rank, world, local_rank):
+    import torch
+
+    import bolt_b200 as B
+    from bolt_b200 import synth
+    from bolt_b200.linear_stack import bert_base_stack
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the B200 arm has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    lib = B.load(build_if_missing=False)
+    B.CHECK_STATUS(lib.bolt_b200_set_device(local_rank))
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    B.CHECK_STATUS(lib.bolt_b200_set_stream(C.c_void_p(stream.cuda_stream)))
+
+    stack = bert_base_stack(M_TOKENS, LAYERS, HIDDEN, INTER, per_channel=True)
+    x_host = torch.from_numpy(synth.normal(1000 + rank, (M_TOKENS, HIDDEN))).reshape(-1).pin_memory()
+    out_host = torch.zeros(M_TOKENS * HIDDEN, dtype=torch.float32).pin_memory()
+    stack.x_dev.copy_(x_host)
+    stack.calibrate()
+    B.CHECK_STATUS(lib.bolt_b200_set_pointer_mode(1))
+    flush = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")  # 2 x L2
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # eager warm-up (also sets kernel attributes before any capture)
+    for _ in range(max(args.warmup, 3)):
+        stack.step()
+    torch.cuda.synchronize()
+    launch_mode = "cuda_graph"
+    g_step = g_gemm = None
+    try:
+        g_step = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_step, stream=stream):
+            stack.step()
+        g_gemm = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_gemm, stream=stream):
+            stack.gemms()
+        g_step.replay()
+        g_gemm.replay()
+        torch.cuda.synchronize()
+    except Exception as e:  # capture refused: time plain stream launches instead
+        launch_mode = "stream (graph capture failed: %s)" % type(e).__name__
+        g_step = g_gemm = None
+    B.CHECK_STATUS(lib.bolt_b200_set_stream(C.c_void_p(stream.cuda_stream)))
+
+    def timed(fn, steps):
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for a, b in evs:
+            flush.fill_(1)          # evict the previous step's lines from L2
+            a.record(stream)
+            fn()
+            b.record(stream)
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in evs) / 1e3
+
+    step_fn = g_step.replay if g_step is not None else stack.step
+    gemm_fn = g_gemm.replay if g_gemm is not None else stack.gemms
+    for _ in range(args.warmup):
+        flush.fill_(1)
+        step_fn()
+    sampler = ClockSampler(local_rank)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    launches0 = lib.bolt_b200_launch_count()
+    wall0 = time.perf_counter()
+    dev_s = timed(step_fn, args.steps)
+    barrier()
+    wall_s = time.perf_counter() - wall0
+    launches = lib.bolt_b200_launch_count() - launches0
+    if g_step is not None:
+        launches = stack.launches_per_step * args.steps  # replays re-launch the captured kernels
+    clocks = sampler.stop() if rank == 0 else None
+    # roofline pass: the GEMM launches alone
+    gemm_s = timed(gemm_fn, args.steps)
+    # end to end through the public host API
+    for _ in range(2):
+        stack.run_host(x_host, out_host)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        flush.fill_(1)
+        torch.cuda.synchronize()
+    flush_s = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        flush.fill_(1)
+        stack.run_host(x_host, out_host)
+    torch.cuda.synchronize()
+    e2e_s = max(time.perf_counter() - t0 - flush_s, 1e-9)
+    status = lib.bolt_b200_device_status()
+
+    vals = torch.tensor([dev_s, gemm_s, e2e_s], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+    dev_s, gemm_s, e2e_s = [float(v) for v in vals.cpu()]
+    if dist is not None:
+        dist.barrier()
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+    peaks, peak_src = measured_peaks()
+    total_ops = OPS_PER_STEP * args.steps * world
+    value = total_ops / dev_s / 1e12
+    n_gemm = 2 * LAYERS
+    gemm_tops = OPS_PER_STEP / (gemm_s / args.steps) / 1e12
+    peak_i8 = 2.0 * peaks["bf16_tflops"]
+    base, _ = cpu_stack_baseline(seconds=12.0) if (world == 1 and not args.no_cpu_baseline) else (None, None)
+    line = {
+        "metric": "int8_gemm_tops", "value": value, "unit": "TOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dev_s / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "u8*s8->s32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "global_tokens": M_TOKENS * world, "parallelism": "dp%d" % world,
+                   "l2": "flushed between timed steps (256 MiB write)", "launch": launch_mode,
+                   "device_status": status, "wall_s_timed_region": wall_s},
+        "e2e": {"value": total_ops / e2e_s / 1e12, "unit": "TOP/s",
+                "h2d_bytes_per_step": M_TOKENS * HIDDEN * 4, "d2h_bytes_per_step": M_TOKENS * HIDDEN * 4,
+                "ms_per_step": e2e_s / args.steps * 1e3},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "roofline": {"bound": "tensor", "achieved": gemm_tops, "peak": peak_i8, "unit": "TFLOP/s",
+                     "frac": gemm_tops / peak_i8, "traffic": GEMM_DRAM_TRAFFIC_PER_LAUNCH,
+                     "kernel": "gemm_u8s8_tcgen05_kernel", "launches_per_step": n_gemm,
+                     "us_per_launch": gemm_s / args.steps / n_gemm * 1e6,
+                     "ops_per_launch": OPS_PER_STEP / n_gemm,
+                     "note": "int8 multiply-add ops (2*M*N*K) in the TFLOP/s slot; peak = 2 x bf16_tflops of "
+                             + peak_src + " (no int8 entry in MEASURED_PEAKS.json); nominal dense int8 is 4500"},
+    }
+    if base is not None:
+        line["cpu_baseline"] = base
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU leg (profiling runs)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+    else:
+        run_b200_arm(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

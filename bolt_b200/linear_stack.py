@@ -1,0 +1,149 @@
+"""A stack of quantized fully-connected layers kept 8-bit between layers -- the serving-side use
+of the GEMM path (what Bolt's FullyConnected operator does per layer on x86,
+compute/tensor/src/fully_connected.cpp:373-411,457-495: u8 activations, s8 pre-packed weights,
+bias folded into offsetC, `scale = {-1, outScale/(scaleI*scaleW)}` for a fused u8 output).
+
+torch is used for device memory and streams only; every kernel is launched by libbolt_b200.so.
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import (CHECK_STATUS, DF_NORMAL, DF_TRANSPOSE, DT_F32, DT_I8, DT_I32, DT_U8_Q, GemmEpilogue, lib,
+               matrix_matrix_multiply_transform_rhs, matrix_matrix_multiply_transform_rhs_bytes, tensor2df)
+
+
+def _torch():
+    import torch
+
+    return torch
+
+
+def quantize_weight_host(W, per_channel):
+    """fp32 [K, N] -> s8 [K, N] and scale(s): 127/absmax per tensor or per output channel, the
+    arithmetic of quantizeF32ToI8 (avx512/quantize.cpp:181-234): rne(x * s) clamped to +-127."""
+    W = np.asarray(W, np.float32)
+    if per_channel:
+        mx = np.abs(W).max(axis=0)
+    else:
+        mx = np.full(W.shape[1], np.abs(W).max(), np.float32)
+    s = np.where(mx == 0, np.float32(1), np.float32(127) / mx).astype(np.float32)
+    q = np.clip(np.rint((W * s[None, :]).astype(np.float32)), -127, 127).astype(np.int8)
+    return q, s
+
+
+class Linear:
+    """One pre-packed layer on the device."""
+
+    def __init__(self, Wq, w_scale, bias=None):
+        torch = _torch()
+        K, N = Wq.shape
+        self.K, self.N = K, N
+        desc = tensor2df(DT_I8, DF_NORMAL, K, N)
+        nbytes, self.rhs_bytes = matrix_matrix_multiply_transform_rhs_bytes(desc)
+        src = torch.from_numpy(np.ascontiguousarray(Wq).view(np.uint8).reshape(-1)).cuda()
+        self.packed = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+        matrix_matrix_multiply_transform_rhs(desc, C.c_void_p(src.data_ptr()), C.c_void_p(self.packed.data_ptr()))
+        torch.cuda.current_stream().synchronize()
+        self.w_scale_host = np.asarray(w_scale, np.float32)
+        self.uniform = bool(np.all(self.w_scale_host == self.w_scale_host[0]))
+        self.w_scale = torch.from_numpy(self.w_scale_host.copy()).cuda()
+        self.bias = bias
+        self.offsetC_ptr = self.packed.data_ptr() + self.rhs_bytes
+
+
+class LinearStack:
+    """x fp32 [M, K0] -> dynamic per-tensor u8 -> L x (u8 x s8 GEMM with fused requantization)
+    -> fp32 [M, N_last].  `out_scales[l]` is the calibrated scale of layer l's u8 output."""
+
+    def __init__(self, layers, M, per_channel=True):
+        torch = _torch()
+        self.layers = layers
+        self.M = M
+        self.per_channel = per_channel
+        self.out_scales = [None] * len(layers)
+        widest = max(max(l.K, l.N) for l in layers)
+        self.act = [torch.zeros(M * widest, dtype=torch.uint8, device="cuda") for _ in range(2)]
+        self.x_dev = torch.zeros(M * layers[0].K, dtype=torch.float32, device="cuda")
+        self.out_dev = torch.zeros(M * layers[-1].N, dtype=torch.float32, device="cuda")
+        self.acc_dev = None
+        self.d_scale = torch.zeros(4, dtype=torch.float32, device="cuda")
+        self.ops_per_step = sum(2 * M * l.K * l.N for l in layers)
+        self.launches_per_step = 3 + len(layers)
+
+    # ---- pieces -------------------------------------------------------------------------
+    def _gemm(self, l, a_ptr, c_ptr, out_dt, out_scale, sA, d_sA=None):
+        ep = GemmEpilogue()
+        ep.out_dt, ep.accumulate, ep.out_scale = out_dt, 0, float(out_scale)
+        ep.sA, ep.sB = float(sA), float(l.w_scale_host[0])
+        ep.d_sA = d_sA
+        ep.row_scale = None
+        ep.col_scale = None if l.uniform else C.c_void_p(l.w_scale.data_ptr())
+        CHECK_STATUS(lib().bolt_b200_gemm_u8s8_ex(l.N, self.M, l.K, C.c_void_p(a_ptr), C.c_void_p(l.packed.data_ptr()),
+                                                  C.c_void_p(l.offsetC_ptr), C.c_void_p(c_ptr), C.byref(ep)), "gemm")
+
+    def quantize_input(self):
+        n = self.M * self.layers[0].K
+        L = lib()
+        CHECK_STATUS(L.bolt_b200_absmax_scale_f32(C.c_void_p(self.x_dev.data_ptr()), n, C.c_void_p(self.d_scale.data_ptr())))
+        CHECK_STATUS(L.bolt_b200_quantize_f32_u8_dev(C.c_void_p(self.x_dev.data_ptr()), n,
+                                                     C.c_void_p(self.act[0].data_ptr()), C.c_void_p(self.d_scale.data_ptr())))
+
+    def gemms(self):
+        """All layers, activations ping-ponging between two device buffers; needs calibrate() first."""
+        cur = 0
+        sA, d_sA = 1.0, C.c_void_p(self.d_scale.data_ptr())
+        last = len(self.layers) - 1
+        for i, l in enumerate(self.layers):
+            if i == last:
+                self._gemm(l, self.act[cur].data_ptr(), self.out_dev.data_ptr(), DT_F32, 1.0, sA, d_sA)
+            else:
+                self._gemm(l, self.act[cur].data_ptr(), self.act[1 - cur].data_ptr(), DT_U8_Q, self.out_scales[i], sA, d_sA)
+                sA, d_sA = self.out_scales[i], None
+                cur = 1 - cur
+
+    def step(self):
+        """One pass, device resident: input already in x_dev, result left in out_dev."""
+        self.quantize_input()
+        self.gemms()
+
+    def calibrate(self):
+        """Sets out_scales from one pass over the current x_dev: each layer's int32 accumulators are
+        dequantized per channel and 127/absmax of the real-valued output becomes its u8 scale."""
+        torch = _torch()
+        self.quantize_input()
+        torch.cuda.synchronize()
+        sA = float(self.d_scale[0].item())
+        cur = 0
+        for i, l in enumerate(self.layers[:-1]):
+            acc = torch.zeros(self.M * l.N, dtype=torch.int32, device="cuda")
+            self._gemm(l, self.act[cur].data_ptr(), acc.data_ptr(), DT_I32, 1.0, 1.0)
+            torch.cuda.synchronize()
+            real = acc.view(self.M, l.N).float() / (np.float32(sA) * l.w_scale[None, :])
+            mx = float(real.abs().max().item())
+            so = float(np.float32(127.0) / np.float32(mx)) if mx > 0 else 1.0
+            self.out_scales[i] = so
+            self._gemm(l, self.act[cur].data_ptr(), self.act[1 - cur].data_ptr(), DT_U8_Q, so, sA)
+            sA, cur = so, 1 - cur
+        torch.cuda.synchronize()
+
+    def run_host(self, x_host, out_host):
+        """End to end from pinned host memory: H2D of the fp32 input, one pass, D2H of the fp32 output."""
+        torch = _torch()
+        self.x_dev.copy_(x_host, non_blocking=True)
+        self.step()
+        out_host.copy_(self.out_dev, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+
+def bert_base_stack(M=4096, layers=12, hidden=768, inter=3072, per_channel=True, seed=100):
+    """BERT-base-shaped linear stack: `layers` x (hidden -> inter -> hidden), weights ~N(0, 0.02)."""
+    from . import synth
+
+    ls = []
+    for i in range(layers):
+        for (k, n, s) in ((hidden, inter, 0), (inter, hidden, 1)):
+            W = synth.normal(seed + 2 * i + s, (k, n), 0.02)
+            q, sc = quantize_weight_host(W, per_channel)
+            ls.append(Linear(q, sc))
+    return LinearStack(ls, M, per_channel)

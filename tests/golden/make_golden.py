@@ -1,0 +1,99 @@
+"""Generates tests/golden/*.npz from the UNMODIFIED reference (oracle/_ref/libbolt_ref.so, built
+from the Bolt sources by `make -C oracle ref`).  Run in a container that has the reference tree
+and an avx512_vnni CPU:
+
+    python tests/golden/make_golden.py
+
+Inputs come from tests/golden/cases.py (seeded, reproducible anywhere); the fixtures hold only the
+reference's outputs, so the checks that use them need neither the reference tree nor AVX512.
+The u8 GEMM outputs are produced one row (M = 1) per call: for M > 1 the reference's AVX512
+kernel strides u8 rows by 4N bytes and overruns its output
+(compute/blas_enhance/src/cpu/x86/int8/avx512/mmm_avx512_vnni.cpp:1468,1473).
+"""
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+sys.path.insert(0, HERE)
+import cases  # noqa: E402
+import oracle as O  # noqa: E402
+from oracle import ptr  # noqa: E402
+
+assert O.ref is not None, "needs oracle/_ref/libbolt_ref.so and an avx512_vnni host"
+
+
+def gemm_outputs():
+    out = {}
+    for i in range(len(cases.GEMM_SHAPES)):
+        m = cases.GEMM_SHAPES[i][0]
+        for a_t, b_t in cases.gemm_variants(i):
+            A, B, Cin = cases.gemm_inputs(i, a_t, b_t)
+            key = "g%d_%d%d" % (i, a_t, b_t)
+            out[key + "_s32"] = O.ref_gemm(A, B, None, Cin, a_t, b_t)
+            if a_t == 0:
+                out[key + "_f32"] = O.ref_gemm(A, B, cases.GEMM_F32_SCALE, None, a_t, b_t)
+                rows = [O.ref_gemm(A[r:r + 1], B, cases.GEMM_U8_SCALE, None, 0, b_t) for r in range(m)]
+                out[key + "_u8"] = np.concatenate(rows)
+    return out
+
+
+def gemv_outputs():
+    out = {}
+    for i in range(len(cases.GEMV_SHAPES)):
+        for w_t in (0, 1):
+            W, x, yin = cases.gemv_inputs(i, w_t)
+            key = "v%d_%d" % (i, w_t)
+            out[key + "_s32"] = O.ref_gemv(W, x, None, yin, w_t)
+            out[key + "_f32"] = O.ref_gemv(W, x, cases.GEMM_F32_SCALE, None, w_t)
+            out[key + "_u8"] = O.ref_gemv(W, x, cases.GEMM_U8_SCALE, None, w_t)
+    return out
+
+
+def quant_outputs():
+    out = {}
+    for i, n in enumerate(cases.QUANT_SIZES):
+        x, a, u, b, off = cases.quant_inputs(i)
+        for name, dst, dt in (("u8", np.uint8, O.DT_U8_Q), ("i8", np.int8, O.DT_I8)):
+            q = np.zeros(n, dst)
+            s = np.array([-1], np.float32)
+            O.ref.ref_quantize(n, O.DT_F32, ptr(x), dt, ptr(q), ptr(s), 0)
+            out["q%d_f32_%s" % (i, name)], out["q%d_f32_%s_scale" % (i, name)] = q, s.copy()
+            q = np.zeros(n, dst)
+            s = np.array([-1, 0.37], np.float32)
+            O.ref.ref_quantize(n, O.DT_I32, ptr(a), dt, ptr(q), ptr(s), 0)
+            out["q%d_i32_%s" % (i, name)], out["q%d_i32_%s_scale" % (i, name)] = q, s.copy()
+            q = np.zeros(n, dst)
+            s = np.array([2.0, 0.37], np.float32)
+            O.ref.ref_quantize(n, O.DT_I32, ptr(a), dt, ptr(q), ptr(s), 0)
+            out["q%d_i32s_%s" % (i, name)] = q
+        q = np.zeros(n, np.int8)
+        O.ref.ref_quantize(n, O.DT_U8_Q, ptr(u), O.DT_I8, ptr(q), None, 0)
+        out["q%d_u8i8" % i] = q
+        s = np.array([0.37], np.float32)
+        ap = np.zeros(n + 64, np.int32)
+        ap[:n] = a
+        f = np.zeros(n + 64, np.float32)  # padded: the reference writes a whole vector when n < 16
+        O.ref.ref_dequantize(n, O.DT_I32, ptr(ap), ptr(s), ptr(f))
+        out["q%d_dq_i32" % i] = f[:n].copy()
+        f = np.zeros(n, np.float32)
+        O.ref.ref_dequantize(n, O.DT_U8_Q, ptr(u), ptr(s), ptr(f))
+        out["q%d_dq_u8" % i] = f
+        r = np.zeros(n, np.int32)
+        O.ref.ref_bias_offsetc(n, ptr(b), ptr(off), 3.0, ptr(r))
+        out["q%d_biasoff" % i] = r
+    return out
+
+
+def main():
+    np.savez_compressed(os.path.join(HERE, "gemm.npz"), **gemm_outputs())
+    np.savez_compressed(os.path.join(HERE, "gemv.npz"), **gemv_outputs())
+    np.savez_compressed(os.path.join(HERE, "quantize.npz"), **quant_outputs())
+    for f in ("gemm.npz", "gemv.npz", "quantize.npz"):
+        print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
+
+
+if __name__ == "__main__":
+    main()

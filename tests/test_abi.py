@@ -1,0 +1,74 @@
+"""The C-ABI library loads without a GPU and exports every symbol include/bolt_b200.h declares;
+the byte-count and format entry points (pure host arithmetic) follow the reference's formulas."""
+import ctypes as C
+import re
+
+import bolt_b200 as B
+
+
+def declared_functions():
+    text = open(B.HEADER_PATH).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    text = text[text.index('extern "C"'):]
+    names = re.findall(r"\b(?:EE|int|void|void \*|uint64_t|DataFormat)\s*\*?\s*([A-Za-z_][A-Za-z0-9_]*)\s*\(", text)
+    return sorted(set(names))
+
+
+def test_every_declared_symbol_is_exported():
+    lib = B.load()
+    names = declared_functions()
+    assert len(names) >= 35
+    for n in names:
+        assert hasattr(lib, n), "libbolt_b200.so lacks %s" % n
+        assert n in B.SIGNATURES, "python binding table lacks %s" % n
+    assert sorted(B.SIGNATURES) == names
+
+
+def test_struct_layouts_match_bolt():
+    assert C.sizeof(B.TensorDesc) == 92          # common/uni/include/tensor_desc.h:93-100
+    assert C.sizeof(B.ConvolutionParamSpec) == 108
+    assert C.sizeof(B.ActivationParamSpec) == 20
+
+
+def test_gemm_byte_counts():
+    """mmm_avx512_vnni.cpp:22-58"""
+    lib = B.load()
+    b, r = C.c_uint32(), C.c_uint32()
+    for N, K in [(768, 768), (3072, 768), (33, 17), (1, 1), (28672, 8192)]:
+        assert lib.matrix_matrix_multiply_transform_rhs_bytes_cuda_b200(N, K, B.DT_I8, B.DF_NORMAL, C.byref(b), C.byref(r)) == 0
+        al = lambda x, a: (x + a - 1) // a * a
+        assert r.value == al(N, 16) * al(K, 8)
+        assert b.value == r.value + 4 * N + 64
+        assert lib.matrix_matrix_multiply_transform_rhs_bytes_cuda_b200(N, K, B.DT_I8, B.DF_NKNxKx, C.byref(b), C.byref(r)) == 0
+        assert (b.value, r.value) == (0, 0)
+    d = B.tensor2df(B.DT_I8, B.DF_TRANSPOSE, 48, 40)   # [N=48, K=40]
+    assert B.matrix_matrix_multiply_transform_rhs_bytes(d) == (48 * 40 + 4 * 48 + 64, 48 * 40)
+    assert lib.b200_matrix_matrix_multiply_rhs_format(B.DT_I8) == B.DF_NKNxKx
+    assert lib.b200_matrix_vector_multiply_weight_format(B.DT_I8) == B.DF_NKN32K4
+    assert lib.b200_matrix_vector_multiply_weight_format(B.DT_U8_Q) == B.DF_NK
+
+
+def test_gemv_byte_counts():
+    """cpu/x86/mvm.cpp:23-41"""
+    d = B.tensor2df(B.DT_I8, B.DF_NORMAL, 100, 33)
+    assert B.matrix_vector_multiply_transform_weight_bytes(d) == 100 * 4 + 112 * 40 + 32
+    d.df = B.DF_NKN32K4
+    assert B.matrix_vector_multiply_transform_weight_bytes(d) == 400
+
+
+def test_wrong_arch_and_type_are_refused():
+    lib = B.load()
+    n = C.c_uint32()
+    a = B.tensor2df(B.DT_U8_Q, B.DF_NORMAL, 4, 8)
+    b = B.tensor2df(B.DT_I8, B.DF_NORMAL, 8, 4)
+    assert lib.b200_matrix_matrix_multiply_tmp_bytes(a, b, C.byref(n), B.X86_AVX512) == B.NOT_SUPPORTED
+    assert lib.b200_matrix_matrix_multiply_tmp_bytes(a, b, C.byref(n), B.CUDA_B200) == B.SUCCESS
+    f = B.tensor2df(B.DT_F32, B.DF_NORMAL, 8, 4)
+    assert lib.b200_matrix_matrix_multiply_transform_rhs_bytes(f, C.byref(n), C.byref(n), B.CUDA_B200) == B.NOT_SUPPORTED
+    # argument checks of mmm.cpp:161-197 come before anything touches the device
+    c = B.tensor2df(B.DT_I32, B.DF_NORMAL, 4, 4)
+    assert lib.b200_matrix_matrix_multiply(a, None, b, None, 0, None, c, None, None, B.CUDA_B200) == B.NULL_POINTER
+    bad = B.tensor2df(B.DT_I32, B.DF_NORMAL, 5, 4)
+    buf = C.create_string_buffer(256)
+    p = C.cast(buf, C.c_void_p)
+    assert lib.b200_matrix_matrix_multiply(a, p, b, p, 64, p, bad, p, None, B.CUDA_B200) == B.NOT_MATCH
