@@ -5,15 +5,17 @@
 // Replaces the AVX512-VNNI micro-kernels and their driver in Bolt
 // (compute/blas_enhance/src/cpu/x86/int8/avx512/mmm_avx512_vnni.cpp:383-1891).
 //
-// One persistent CTA per SM, 192 threads, three roles:
+// One persistent CTA per SM, 320 threads, three roles:
 //   warp 0      TMA producer: cp.async.bulk.tensor 2-D loads of a 128 x 128-byte A tile and a
 //               BLOCK_N x 128-byte B tile per pipeline stage, 128-byte swizzle, mbarrier complete_tx
 //   warp 1      MMA issuer: one thread issues tcgen05.mma.cta_group::1.kind::i8 (M=128, N=BLOCK_N,
 //               K=32 per instruction, A unsigned / B signed, int32 accumulate, no saturation) with
 //               shared-memory matrix descriptors; accumulators live in tensor memory (2 x 256 columns,
 //               so the epilogue of tile i overlaps the main loop of tile i+1)
-//   warps 2..5  epilogue: tcgen05.ld 32 lanes x 32 columns per warp, fused offsetC / C_in add and the
-//               reference's s32 -> f32 / u8 conversions, direct 16-byte global stores
+//   warps 2..9  epilogue, two warps per scheduler: the pair that shares a tensor-memory lane quadrant
+//               splits the tile's columns; tcgen05.ld of 32 lanes x 32 columns, software pipelined
+//               (the next chunk is in flight while this one is converted), fused offsetC / C_in add and
+//               the reference's s32 -> f32 / u8 conversions, 16-byte global stores
 // Every mbarrier wait is bounded; a wait that runs out sets the device status word and the CTA
 // drains and exits (tensor memory is always released).
 #include <cuda.h>
@@ -28,24 +30,25 @@ constexpr int BLOCK_K = 128;         // bytes of K per stage = one 128B swizzle 
 constexpr int MAX_BLOCK_N = 256;
 constexpr int STAGES = 4;
 constexpr int UMMA_K = 32;           // K per tcgen05.mma.kind::i8
-constexpr int NUM_THREADS = 192;
-constexpr int EPI_THREADS = 128;
+constexpr int EPI_WARPS = 8;
+constexpr int EPI_THREADS = EPI_WARPS * 32;
+constexpr int NUM_THREADS = 64 + EPI_THREADS;
 constexpr uint32_t TMEM_COLS = 512;  // 2 accumulators x 256 columns
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // per wait; far above any legitimate wait
 
 constexpr int SMEM_A_STAGE = BLOCK_M * BLOCK_K;        // 16 KiB
 constexpr int SMEM_B_STAGE = MAX_BLOCK_N * BLOCK_K;    // 32 KiB
 
-struct __align__(8) SmemCtl {
+struct __align__(16) SmemCtl {
     uint64_t full[STAGES];
     uint64_t empty[STAGES];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
-    // per epilogue warp, double buffered by accumulator: column constants of the current tile
-    int32_t offs[4][2][MAX_BLOCK_N];
-    float colf[4][2][MAX_BLOCK_N];
+    // column constants of the current tile, double buffered by accumulator
+    __align__(16) int32_t offs[2][MAX_BLOCK_N];
+    __align__(16) float colf[2][MAX_BLOCK_N];
 };
 
 constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * (SMEM_A_STAGE + SMEM_B_STAGE) +
@@ -159,9 +162,27 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
         : "r"(taddr)
         : "memory");
 }
-__device__ __forceinline__ void tmem_ld_wait()
+// The registers are listed as read-write operands so that no use of them can be scheduled above
+// the wait (tcgen05.ld delivers them asynchronously).
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32])
 {
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+                   "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
+                   "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
+                   "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :
+                 : "memory");
+}
+// usat8( rne(f) + 128 ) without a float->int conversion instruction: adding 1.5 * 2^23 rounds f to
+// an integer (nearest even) in the low mantissa bits; the integer subtraction removes the bias and
+// adds the zero point.  rne(f) in [-128, 127] maps to 0..255; every other input (large, negative
+// below -128, NaN, infinity) leaves a word above 255, which the unsigned clamp turns into 255 --
+// exactly what vcvtps2dq + vpaddd 128 + vpmovusdb store.
+__device__ __forceinline__ uint32_t f32_to_u8_zp128(float f)
+{
+    return min(__float_as_uint(__fadd_rn(f, 12582912.0f)) - (0x4B400000u - 128u), 255u);
 }
 
 // Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows of 128 bytes, groups of
@@ -183,18 +204,75 @@ __device__ __forceinline__ uint32_t make_idesc_i8(uint32_t n)
     return (2u << 4) | (0u << 7) | (1u << 10) | ((n >> 3) << 17) | ((uint32_t)(BLOCK_M >> 4) << 24);
 }
 
-// ---- epilogue for 32 consecutive columns of one row --------------------------------------------
+// ---- epilogue for 32 consecutive columns of one row: the common case ---------------------------
+// Full, 16-byte aligned chunk, C overwritten, one conversion factor per column.  Kept free of
+// branches and small, because each epilogue warp runs it 4 to 8 times per tile back to back and
+// the instruction stream has to stay resident.  Per element: add offsetC, s32 -> f32 (vcvtdq2ps),
+// multiply (vmulps), then for u8 the bias-add rounding of f32_to_u8_zp128.
+template <int KIND>
+__device__ __forceinline__ void store_chunk_fast(void *C, uint32_t N, const int32_t *offs, const float *colf,
+    uint32_t m, uint32_t n0, uint32_t cl, const uint32_t (&r)[32])
+{
+    const size_t row_off = (size_t)m * N + n0;
+    if (KIND == 2) {
+        uint32_t w[8];
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            const int4 o = *reinterpret_cast<const int4 *>(offs + cl + j);
+            const float4 c4 = *reinterpret_cast<const float4 *>(colf + cl + j);
+            const uint32_t b0 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j] + o.x), c4.x));
+            const uint32_t b1 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j + 1] + o.y), c4.y));
+            const uint32_t b2 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j + 2] + o.z), c4.z));
+            const uint32_t b3 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j + 3] + o.w), c4.w));
+            w[j >> 2] = b0 + (b1 << 8) + (b2 << 16) + (b3 << 24);
+        }
+        uint8_t *out = reinterpret_cast<uint8_t *>(C) + row_off;
+        *reinterpret_cast<uint4 *>(out) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4 *>(out + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+    } else if (KIND == 1) {
+        float *out = reinterpret_cast<float *>(C) + row_off;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            const int4 o = *reinterpret_cast<const int4 *>(offs + cl + j);
+            const float4 c4 = *reinterpret_cast<const float4 *>(colf + cl + j);
+            *reinterpret_cast<float4 *>(out + j) = make_float4(acc_to_f32((int)r[j] + o.x, c4.x),
+                acc_to_f32((int)r[j + 1] + o.y, c4.y), acc_to_f32((int)r[j + 2] + o.z, c4.z),
+                acc_to_f32((int)r[j + 3] + o.w, c4.w));
+        }
+    } else {
+        int32_t *out = reinterpret_cast<int32_t *>(C) + row_off;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            const int4 o = *reinterpret_cast<const int4 *>(offs + cl + j);
+            *reinterpret_cast<int4 *>(out + j) =
+                make_int4((int)r[j] + o.x, (int)r[j + 1] + o.y, (int)r[j + 2] + o.z, (int)r[j + 3] + o.w);
+        }
+    }
+}
+
+// ---- epilogue for 32 consecutive columns of one row: every other case ---------------------------
+// (ragged or unaligned N, accumulate into C, per-row scales)
 __device__ __forceinline__ void store_chunk(const Params &p, const int32_t *offs, const float *colf, uint32_t m,
-    uint32_t n0 /*global col of r[0]*/, uint32_t cl /*tile-local col of r[0]*/, uint32_t (&r)[32])
+    uint32_t n0 /*global col of r[0]*/, uint32_t cl /*tile-local col of r[0]*/, const uint32_t (&r)[32])
 {
     const GemmEpilogue &ep = p.ep;
     const uint32_t ncols = min(32u, p.N - n0);
     const size_t row_off = (size_t)m * p.N + n0;
     const bool full_vec = p.vec_ok && ncols == 32;
     int acc[32];
+    float cf[32];
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-        acc[j] = (int)r[j] + offs[cl + j];
+    for (int j = 0; j < 32; j += 4) {
+        const int4 o = *reinterpret_cast<const int4 *>(offs + cl + j);
+        const float4 c4 = *reinterpret_cast<const float4 *>(colf + cl + j);
+        acc[j] = (int)r[j] + o.x;
+        acc[j + 1] = (int)r[j + 1] + o.y;
+        acc[j + 2] = (int)r[j + 2] + o.z;
+        acc[j + 3] = (int)r[j + 3] + o.w;
+        cf[j] = c4.x;
+        cf[j + 1] = c4.y;
+        cf[j + 2] = c4.z;
+        cf[j + 3] = c4.w;
     }
     if (ep.out_kind != 2 && ep.accumulate) {
         const int32_t *cin = reinterpret_cast<const int32_t *>(p.C) + row_off;
@@ -244,7 +322,7 @@ __device__ __forceinline__ void store_chunk(const Params &p, const int32_t *offs
         float f[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-            float fac = colf[cl + j];
+            float fac = cf[j];
             if (per_elem) {
                 fac = __fdiv_rn(ep.num, __fmul_rn(rs, fac));
             }
@@ -272,11 +350,11 @@ __device__ __forceinline__ void store_chunk(const Params &p, const int32_t *offs
         uint32_t b[4];
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
-            float fac = colf[cl + j + t];
+            float fac = cf[j + t];
             if (per_elem) {
                 fac = __fdiv_rn(ep.num, __fmul_rn(rs, fac));
             }
-            b[t] = acc_to_u8(acc[j + t], fac);
+            b[t] = f32_to_u8_zp128(__fmul_rn(__int2float_rn(acc[j + t]), fac));
         }
         w[j >> 2] = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
     }
@@ -293,6 +371,8 @@ __device__ __forceinline__ void store_chunk(const Params &p, const int32_t *offs
     }
 }
 
+// KIND >= 0: the fast epilogue for that output kind (0 s32, 1 f32, 2 u8); KIND < 0: the general one.
+template <int KIND>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
     const Params p)
@@ -360,6 +440,7 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 atomicExch(&ctl->abort_flag, 1u);
             }
         }
+        __syncwarp();
     } else if (warp == 1) {
         // ------------------------------- MMA issuer ---------------------------------------------
         if (lane == 0) {
@@ -406,23 +487,27 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 atomicExch(&ctl->abort_flag, 1u);
             }
         }
+        __syncwarp();
     } else {
-        // ------------------------------- epilogue warps 2..5 ------------------------------------
-        const uint32_t quad = warp & 3;  // tensor-memory lane quadrant this warp may read
-        const uint32_t ew = warp - 2;    // 0..3: which private copy of the column constants
+        // ------------------------------- epilogue warps 2..9 ------------------------------------
+        const uint32_t quad = warp & 3;         // tensor-memory lane quadrant this warp may read
+        const uint32_t half = (warp - 2) >> 2;  // which half of the tile's columns
+        const uint32_t et = threadIdx.x - 64;   // 0..255
         const GemmEpilogue &ep = p.ep;
+        const uint32_t nch = p.block_n >> 5;
+        const uint32_t c_begin = half ? ((nch + 1) >> 1) : 0u;
+        const uint32_t c_end = half ? nch : ((nch + 1) >> 1);
         uint32_t it = 0;
-        bool ok = true;
         for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
             const uint32_t acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
             const uint32_t m0 = (tile % p.tiles_m) * BLOCK_M;
             const uint32_t n0 = (tile / p.tiles_m) * p.block_n;
-            // per-tile column constants -> this warp's shared-memory copy (double buffered by `acc`,
-            // so only a warp-level sync is needed)
-            int32_t *offs = ctl->offs[ew][acc];
-            float *colf = ctl->colf[ew][acc];
-            for (uint32_t j = lane; j < p.block_n; j += 32) {
+            // per-tile column constants -> shared memory (double buffered by `acc`: the barrier of
+            // tile i+1 separates the last reads of tile i from the writes of tile i+2)
+            int32_t *offs = ctl->offs[acc];
+            float *colf = ctl->colf[acc];
+            for (uint32_t j = et; j < p.block_n; j += EPI_THREADS) {
                 const uint32_t n = n0 + j;
                 int32_t o = 0;
                 float f = ep.factor;
@@ -440,28 +525,69 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 offs[j] = o;
                 colf[j] = f;
             }
-            __syncwarp();
-            ok = mbar_wait(&ctl->tmem_full[acc], acc_phase);
+            // every epilogue thread takes part in this barrier once per tile; a warp whose wait ran
+            // out keeps arriving here, and all of them leave together once the flag is visible
+            asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+            if (*reinterpret_cast<volatile uint32_t *>(&ctl->abort_flag) != 0) {
+                break;
+            }
+            bool ok = mbar_wait(&ctl->tmem_full[acc], acc_phase);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
-                break;
+                if (lane == 0) {
+                    atomicExch(p.status, 3);
+                    atomicExch(&ctl->abort_flag, 1u);
+                }
+                continue;
             }
             tcgen05_fence_after();
             const uint32_t m = m0 + quad * 32 + lane;
-            for (uint32_t c = 0; c < p.block_n; c += 32) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((quad * 32u) << 16) + acc * MAX_BLOCK_N + c, r);
-                tmem_ld_wait();
-                if (m < p.M && n0 + c < p.N) {
-                    store_chunk(p, offs, colf, m, n0 + c, c, r);
+            const uint32_t tbase = tmem_base + ((quad * 32u) << 16) + acc * MAX_BLOCK_N;
+            const bool row_ok = m < p.M;
+            uint32_t ra[32], rb[32];
+            if (c_begin < c_end) {
+                tmem_ld32(tbase + c_begin * 32, ra);
+            }
+            bool released = false;
+            for (uint32_t c = c_begin; c < c_end; c += 2) {
+                tmem_ld_wait(ra);
+                const bool has1 = c + 1 < c_end;
+                if (has1) {
+                    tmem_ld32(tbase + (c + 1) * 32, rb);
+                } else {
+                    tcgen05_fence_before();
+                    mbar_arrive(&ctl->tmem_empty[acc]);  // accumulator fully read: the MMA may reuse it
+                    released = true;
+                }
+                if (row_ok && n0 + c * 32 < p.N) {
+                    if (KIND >= 0) {
+                        store_chunk_fast<KIND>(p.C, p.N, offs, colf, m, n0 + c * 32, c * 32, ra);
+                    } else {
+                        store_chunk(p, offs, colf, m, n0 + c * 32, c * 32, ra);
+                    }
+                }
+                if (has1) {
+                    tmem_ld_wait(rb);
+                    if (c + 2 < c_end) {
+                        tmem_ld32(tbase + (c + 2) * 32, ra);
+                    } else {
+                        tcgen05_fence_before();
+                        mbar_arrive(&ctl->tmem_empty[acc]);
+                        released = true;
+                    }
+                    if (row_ok && n0 + (c + 1) * 32 < p.N) {
+                        if (KIND >= 0) {
+                            store_chunk_fast<KIND>(p.C, p.N, offs, colf, m, n0 + (c + 1) * 32, (c + 1) * 32, rb);
+                        } else {
+                            store_chunk(p, offs, colf, m, n0 + (c + 1) * 32, (c + 1) * 32, rb);
+                        }
+                    }
                 }
             }
-            tcgen05_fence_before();
-            mbar_arrive(&ctl->tmem_empty[acc]);
-        }
-        if (!ok && lane == 0) {
-            atomicExch(p.status, 3);
-            atomicExch(&ctl->abort_flag, 1u);
+            if (!released) {
+                tcgen05_fence_before();
+                mbar_arrive(&ctl->tmem_empty[acc]);
+            }
         }
     }
 
@@ -570,8 +696,14 @@ EE launch_gemm_tcgen05(uint32_t M, uint32_t N, uint32_t K, const uint8_t *A, con
     static std::once_flag attr_once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(attr_once, [] {
-        attr_err = cudaFuncSetAttribute(
-            gemm_u8s8_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        const void *kernels[4] = {(const void *)gemm_u8s8_tcgen05_kernel<-1>, (const void *)gemm_u8s8_tcgen05_kernel<0>,
+            (const void *)gemm_u8s8_tcgen05_kernel<1>, (const void *)gemm_u8s8_tcgen05_kernel<2>};
+        for (const void *k : kernels) {
+            cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+            if (e != cudaSuccess) {
+                attr_err = e;
+            }
+        }
     });
     B200_CUDA(attr_err);
 
@@ -596,7 +728,19 @@ EE launch_gemm_tcgen05(uint32_t M, uint32_t N, uint32_t K, const uint8_t *A, con
     }
     const uint32_t tiles = p.tiles_m * p.tiles_n;
     const uint32_t grid = tiles < (uint32_t)c->sm_count ? tiles : (uint32_t)c->sm_count;
-    gemm_u8s8_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
+    // the fast epilogue needs whole, 16-byte aligned 32-column chunks, no read of C and one
+    // conversion factor per column
+    const bool fast = p.vec_ok && (N % 32 == 0) && !(ep.out_kind != 2 && ep.accumulate) &&
+        !(ep.per_channel && ep.row_scale != nullptr);
+    if (!fast) {
+        gemm_u8s8_tcgen05_kernel<-1><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
+    } else if (ep.out_kind == 0) {
+        gemm_u8s8_tcgen05_kernel<0><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
+    } else if (ep.out_kind == 1) {
+        gemm_u8s8_tcgen05_kernel<1><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
+    } else {
+        gemm_u8s8_tcgen05_kernel<2><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
+    }
     count_launch();
     B200_CUDA(cudaGetLastError());
     return SUCCESS;
