@@ -497,39 +497,63 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         const uint32_t nch = p.block_n >> 5;
         const uint32_t c_begin = half ? ((nch + 1) >> 1) : 0u;
         const uint32_t c_end = half ? nch : ((nch + 1) >> 1);
+        // Column constants (offsetC and the conversion factor) of a tile live in shared memory,
+        // double buffered by accumulator.  Thread `et` owns column `et`: it fetches the next tile's
+        // values into registers before it waits for the current accumulator, and parks them in the
+        // other buffer after the tile, so the global-load latency never sits on the critical path.
+        // The loads are volatile asm so that they stay where they are written (early); everything
+        // that depends on them is written after the tile's chunks (late).
+        auto fetch_raw = [&](uint32_t tile_n0, int32_t &o, float &sb) {
+            o = 0;
+            sb = ep.sB;
+            const uint32_t n = tile_n0 + et;
+            if (et < p.block_n && n < p.N) {
+                if (ep.offsetC != nullptr) {
+                    asm volatile("ld.global.nc.b32 %0, [%1];" : "=r"(o) : "l"(ep.offsetC + n));
+                }
+                if (ep.per_channel && ep.col_scale != nullptr) {
+                    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(sb) : "l"(ep.col_scale + n));
+                }
+            }
+        };
+        float sa_dev = ep.sA;
+        if (ep.per_channel && ep.sA_dev != nullptr) {
+            asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(sa_dev) : "l"(ep.sA_dev));
+        }
+        auto factor_of = [&](float sb) {
+            if (!ep.per_channel) {
+                return ep.factor;
+            }
+            // with per-row scales the division is done per element; keep sB here
+            return ep.row_scale ? sb : __fdiv_rn(ep.num, __fmul_rn(sa_dev, sb));
+        };
+        if (blockIdx.x < num_tiles) {
+            int32_t o;
+            float sb;
+            fetch_raw((blockIdx.x / p.tiles_m) * p.block_n, o, sb);
+            ctl->offs[0][et] = o;
+            ctl->colf[0][et] = factor_of(sb);
+        }
         uint32_t it = 0;
         for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
             const uint32_t acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
             const uint32_t m0 = (tile % p.tiles_m) * BLOCK_M;
             const uint32_t n0 = (tile / p.tiles_m) * p.block_n;
-            // per-tile column constants -> shared memory (double buffered by `acc`: the barrier of
-            // tile i+1 separates the last reads of tile i from the writes of tile i+2)
-            int32_t *offs = ctl->offs[acc];
-            float *colf = ctl->colf[acc];
-            for (uint32_t j = et; j < p.block_n; j += EPI_THREADS) {
-                const uint32_t n = n0 + j;
-                int32_t o = 0;
-                float f = ep.factor;
-                if (n < p.N) {
-                    if (ep.offsetC != nullptr) {
-                        o = ep.offsetC[n];
-                    }
-                    if (ep.per_channel) {
-                        const float sb = ep.col_scale ? ep.col_scale[n] : ep.sB;
-                        // with per-row scales the division is done per element; keep sB here
-                        const float sa = ep.sA_dev ? *ep.sA_dev : ep.sA;
-                        f = ep.row_scale ? sb : __fdiv_rn(ep.num, __fmul_rn(sa, sb));
-                    }
-                }
-                offs[j] = o;
-                colf[j] = f;
-            }
-            // every epilogue thread takes part in this barrier once per tile; a warp whose wait ran
-            // out keeps arriving here, and all of them leave together once the flag is visible
+            const int32_t *offs = ctl->offs[acc];
+            const float *colf = ctl->colf[acc];
+            // Once per tile, all epilogue threads: makes this tile's constants visible and proves that
+            // everyone is done with the other buffer.  A warp whose wait ran out keeps arriving here,
+            // and all of them leave together once the flag is visible.
             asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
             if (*reinterpret_cast<volatile uint32_t *>(&ctl->abort_flag) != 0) {
                 break;
+            }
+            const uint32_t next_tile = tile + gridDim.x;
+            int32_t o_next = 0;
+            float sb_next = 0.f;
+            if (next_tile < num_tiles) {
+                fetch_raw((next_tile / p.tiles_m) * p.block_n, o_next, sb_next);
             }
             bool ok = mbar_wait(&ctl->tmem_full[acc], acc_phase);
             ok = __all_sync(0xffffffffu, ok);
@@ -587,6 +611,10 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             if (!released) {
                 tcgen05_fence_before();
                 mbar_arrive(&ctl->tmem_empty[acc]);
+            }
+            if (next_tile < num_tiles) {
+                ctl->offs[acc ^ 1][et] = o_next;
+                ctl->colf[acc ^ 1][et] = factor_of(sb_next);
             }
         }
     }
