@@ -255,3 +255,80 @@ def dequantize(qDesc, qData, scale, dDesc, dData):
     b = tensor1d(DT_F32, 0)
     CHECK_STATUS(lib().dequantize_cuda_b200(C.byref(qDesc), qData, C.cast(arr, _f32p), C.byref(b), None,
                                             C.byref(dDesc), dData), "dequantize")
+
+
+# ---- convolution (compute/tensor/include/tensor_computing.h:26-64) --------------------------
+def conv_param(oc, fh, fw, stride=1, pad=0, dilation=1, relu=False):
+    """ConvolutionParamSpec for a plain 2-D convolution (group 1)."""
+    p = ConvolutionParamSpec()
+    p.num_outputs = p.num_outputs_origin = oc
+    p.kernel_t, p.kernel_h, p.kernel_w = 1, fh, fw
+    p.stride_t, p.stride_h, p.stride_w = 1, stride, stride
+    p.pad_top = p.pad_bottom = p.pad_left = p.pad_right = pad
+    p.group = 1
+    p.dilatedRate_t, p.dilatedRate_h, p.dilatedRate_w = 1, dilation, dilation
+    p.pw_activation_type = ACTIVATION_RELU if relu else ACTIVATION_NULL
+    return p
+
+
+def convolution_infer_output_size(inputDesc, filterDesc, p, target_dt):
+    """compute/tensor/src/convolution.cpp:28-145 for the CPU layouts: output format NCHWc16 for a
+    u8 target with more than 8 output channels, NCHWc8 otherwise (:98-103)."""
+    iw, ih, ic, n = inputDesc.dims[0], inputDesc.dims[1], inputDesc.dims[2], inputDesc.dims[3]
+    fw, fh, fn = filterDesc.dims[0], filterDesc.dims[1], filterDesc.dims[3]
+    oh = (ih + p.pad_top + p.pad_bottom - ((fh - 1) * p.dilatedRate_h + 1)) // p.stride_h + 1
+    ow = (iw + p.pad_left + p.pad_right - ((fw - 1) * p.dilatedRate_w + 1)) // p.stride_w + 1
+    if fn % 8 != 0:
+        raise BoltError(NOT_SUPPORTED, "convolution_infer_output_size")
+    df = DF_NCHWC16 if (target_dt == DT_U8_Q and fn != 8) else DF_NCHWC8
+    return tensor4df(target_dt, df, n, fn, oh, ow)
+
+
+def convolution_infer_forward_algorithm(inputDesc, filterDesc, outputDesc, p, target_dt):
+    alg = C.c_uint32(CONVOLUTION_ALGORITHM_NULL)
+    CHECK_STATUS(lib().convolution_infer_forward_algorithm_cuda_b200(
+        C.byref(inputDesc), C.byref(filterDesc), C.byref(outputDesc), C.byref(p), 1, C.byref(alg), target_dt),
+        "convolution_infer_forward_algorithm")
+    return alg.value
+
+
+def convolution_transform_filter_bytes(filterDesc, p, alg):
+    n = C.c_uint32(0)
+    CHECK_STATUS(lib().convolution_transform_filter_bytes_cuda_b200(C.byref(filterDesc), C.byref(p), alg, C.byref(n)),
+                 "convolution_transform_filter_bytes")
+    return n.value
+
+
+def convolution_transform_filter(filterDesc, filter_ptr, p, alg, dst_ptr):
+    out = TensorDesc()
+    CHECK_STATUS(lib().convolution_transform_filter_cuda_b200(C.byref(filterDesc), filter_ptr, C.byref(p), alg,
+                                                              C.byref(out), dst_ptr), "convolution_transform_filter")
+    return out
+
+
+def convolution_infer_forward_tmp_bytes(inputDesc, ftmDesc, outputDesc, p, alg):
+    n = C.c_uint32(0)
+    CHECK_STATUS(lib().convolution_infer_forward_tmp_bytes_cuda_b200(
+        C.byref(inputDesc), C.byref(ftmDesc), C.byref(outputDesc), C.byref(p), alg, C.byref(n)),
+        "convolution_infer_forward_tmp_bytes")
+    return n.value
+
+
+def convolution(inputDesc, input_ptr, ftmDesc, filter_ptr, p, alg, scale, bias_ptr, tmp_bytes, tmp_ptr, outputDesc,
+                output_ptr, relu=False, eltwise_ptr=None):
+    """`scale`: for int8 a 3-float list {input, output, filter} updated in place (convolution_cpu.hpp:142-157);
+    for 1-bit filters a device/host pointer to the fp16 per-channel scales."""
+    act = ActivationParamSpec()
+    act.mode = ACTIVATION_RELU if relu else ACTIVATION_NULL
+    sd, bd = tensor1d(DT_F32, 3), tensor1d(DT_F32, outputDesc.dims[2])
+    if isinstance(scale, list):
+        arr = (C.c_float * len(scale))(*scale)
+        sp = C.cast(arr, C.c_void_p)
+    else:
+        arr, sp = None, scale
+    CHECK_STATUS(lib().convolution_cuda_b200(C.byref(inputDesc), input_ptr, eltwise_ptr, C.byref(ftmDesc), filter_ptr,
+                                             C.byref(p), alg, C.byref(sd), sp, C.byref(bd), bias_ptr, tmp_bytes, tmp_ptr,
+                                             C.byref(outputDesc), output_ptr, C.byref(act)), "convolution")
+    if arr is not None:
+        for i in range(len(scale)):
+            scale[i] = arr[i]

@@ -136,6 +136,12 @@ EE cuda_ee(cudaError_t e);
         }                      \
     } while (0)
 
+// cuTensorMapEncodeTiled (found through the runtime's driver entry point) for byte tensors of
+// rank <= 5; zero fill out of range.  `map` points at a CUtensorMap.
+bool tensor_map_encoder_available();
+bool encode_tiled_u8(void *map, uint32_t rank, const void *base, const uint64_t *dims, const uint64_t *strides,
+    const uint32_t *box, const uint32_t *elem_strides, bool swizzle128);
+
 // ---- kernel launchers (device pointers only) ----------------------------------------------
 struct GemmEpilogue {
     int out_kind;              // 0 int32, 1 fp32, 2 u8

@@ -1,32 +1,133 @@
-// conv.cu -- int8 and 1-bit convolution entry points.
+// conv.cu -- convolution entry points: dispatch on the filter type to the int8 implicit-GEMM path
+// (conv_i8.cu) or the 1-bit path (bnn.cu), as Bolt's convolution dispatchers do
+// (compute/tensor/src/convolution.cpp:367-470, cpu/x86/convolution.cpp:233-363,
+//  cpu/arm/convolution.cpp:492-494).
 #include "common.cuh"
+
+namespace b200 {
+EE conv_i8_transform_filter_bytes(const TensorDesc *filterDesc, U32 *bytes);
+EE conv_i8_transform_filter(const TensorDesc *filterDesc, const void *filter, TensorDesc *ftmDesc, void *dst);
+EE conv_i8_tmp_bytes(const TensorDesc *inputDesc, const TensorDesc *filterDesc, const TensorDesc *outputDesc,
+    const ConvolutionParamSpec *cp, U32 *bytes);
+EE conv_i8_run(const TensorDesc *inputDesc, void *input, void *eltwiseInput, const TensorDesc *filterDesc,
+    const void *filter, const ConvolutionParamSpec *cp, void *scale, const void *bias, U32 tmpBytes, void *tmp,
+    const TensorDesc *outputDesc, void *output, const ActivationParamSpec *act);
+EE bnn_transform_filter_bytes(const TensorDesc *filterDesc, U32 *bytes);
+EE bnn_transform_filter(const TensorDesc *filterDesc, const void *filter, TensorDesc *ftmDesc, void *dst);
+EE bnn_tmp_bytes(const TensorDesc *inputDesc, const TensorDesc *filterDesc, const TensorDesc *outputDesc,
+    const ConvolutionParamSpec *cp, U32 *bytes);
+EE bnn_run(const TensorDesc *inputDesc, const void *input, const TensorDesc *filterDesc, const void *filter,
+    const ConvolutionParamSpec *cp, const void *scale, const void *bias, U32 tmpBytes, void *tmp,
+    const TensorDesc *outputDesc, void *output);
+}  // namespace b200
+
+using namespace b200;
+
+namespace {
+bool is_bnn(DataType dt)
+{
+    return dt == DT_BIN01 || dt == DT_BIN11;
+}
+}  // namespace
 
 extern "C" {
 
-EE convolution_infer_forward_algorithm_cuda_b200(const TensorDesc *, const TensorDesc *, const TensorDesc *,
-    const ConvolutionParamSpec *, ConvolutionPolicy, ConvolutionForwardAlgorithm *, DataType)
+EE convolution_infer_forward_algorithm_cuda_b200(const TensorDesc *inputDesc, const TensorDesc *filterDesc,
+    const TensorDesc *outputDesc, const ConvolutionParamSpec *convParamSpec, ConvolutionPolicy policy,
+    ConvolutionForwardAlgorithm *algorithm, DataType targetDataType)
 {
-    return NOT_IMPLEMENTED;
+    (void)inputDesc;
+    (void)outputDesc;
+    (void)policy;
+    (void)targetDataType;
+    if (filterDesc == nullptr || convParamSpec == nullptr || algorithm == nullptr) {
+        return NULL_POINTER;
+    }
+    if (*algorithm != CONVOLUTION_ALGORITHM_NULL) {
+        return SUCCESS;  // a preset algorithm is honoured (convolution.cpp:158-160)
+    }
+    if (filterDesc->nDims != 4) {
+        return NOT_SUPPORTED;
+    }
+    if (is_bnn(filterDesc->dt)) {
+        *algorithm = CONVOLUTION_ALGORITHM_BNN;
+    } else if (filterDesc->dims[0] == 1 && filterDesc->dims[1] == 1) {
+        *algorithm = CONVOLUTION_ALGORITHM_POINTWISE;  // cpu/x86/convolution.cpp:60-62
+    } else {
+        *algorithm = CONVOLUTION_ALGORITHM_DIRECT;
+    }
+    return SUCCESS;
 }
-EE convolution_transform_filter_bytes_cuda_b200(
-    const TensorDesc *, const ConvolutionParamSpec *, ConvolutionForwardAlgorithm, U32 *)
+
+EE convolution_transform_filter_bytes_cuda_b200(const TensorDesc *filterDesc, const ConvolutionParamSpec *convParamSpec,
+    ConvolutionForwardAlgorithm algorithm, U32 *bytes)
 {
-    return NOT_IMPLEMENTED;
+    (void)convParamSpec;
+    (void)algorithm;
+    if (filterDesc == nullptr || bytes == nullptr) {
+        return NULL_POINTER;
+    }
+    if (is_bnn(filterDesc->dt)) {
+        return bnn_transform_filter_bytes(filterDesc, bytes);
+    }
+    if (filterDesc->dt != DT_I8) {
+        return NOT_SUPPORTED;
+    }
+    return conv_i8_transform_filter_bytes(filterDesc, bytes);
 }
-EE convolution_transform_filter_cuda_b200(const TensorDesc *, const void *, const ConvolutionParamSpec *,
-    ConvolutionForwardAlgorithm, TensorDesc *, void *)
+
+EE convolution_transform_filter_cuda_b200(const TensorDesc *filterDesc, const void *filter,
+    const ConvolutionParamSpec *convParamSpec, ConvolutionForwardAlgorithm algorithm, TensorDesc *ftmDesc,
+    void *filterTransformed)
 {
-    return NOT_IMPLEMENTED;
+    (void)algorithm;
+    if (filterDesc == nullptr || ftmDesc == nullptr) {
+        return NULL_POINTER;
+    }
+    if (convParamSpec != nullptr && convParamSpec->group > 1) {
+        return NOT_SUPPORTED;
+    }
+    if (is_bnn(filterDesc->dt)) {
+        return bnn_transform_filter(filterDesc, filter, ftmDesc, filterTransformed);
+    }
+    if (filterDesc->dt != DT_I8) {
+        return NOT_SUPPORTED;
+    }
+    return conv_i8_transform_filter(filterDesc, filter, ftmDesc, filterTransformed);
 }
-EE convolution_infer_forward_tmp_bytes_cuda_b200(const TensorDesc *, const TensorDesc *, const TensorDesc *,
-    const ConvolutionParamSpec *, ConvolutionForwardAlgorithm, U32 *)
+
+EE convolution_infer_forward_tmp_bytes_cuda_b200(const TensorDesc *inputDesc, const TensorDesc *filterDesc,
+    const TensorDesc *outputDesc, const ConvolutionParamSpec *convParamSpec, ConvolutionForwardAlgorithm algorithm,
+    U32 *bytes)
 {
-    return NOT_IMPLEMENTED;
+    (void)algorithm;
+    if (inputDesc == nullptr || filterDesc == nullptr || outputDesc == nullptr || convParamSpec == nullptr) {
+        return NULL_POINTER;
+    }
+    if (is_bnn(filterDesc->dt)) {
+        return bnn_tmp_bytes(inputDesc, filterDesc, outputDesc, convParamSpec, bytes);
+    }
+    return conv_i8_tmp_bytes(inputDesc, filterDesc, outputDesc, convParamSpec, bytes);
 }
-EE convolution_cuda_b200(const TensorDesc *, void *, void *, const TensorDesc *, const void *,
-    const ConvolutionParamSpec *, ConvolutionForwardAlgorithm, const TensorDesc *, void *, const TensorDesc *,
-    const void *, U32, void *, const TensorDesc *, void *, const ActivationParamSpec *)
+
+EE convolution_cuda_b200(const TensorDesc *inputDesc, void *input, void *eltwiseInput, const TensorDesc *filterDesc,
+    const void *filter, const ConvolutionParamSpec *convParamSpec, ConvolutionForwardAlgorithm algorithm,
+    const TensorDesc *scaleDesc, void *scale, const TensorDesc *biasDesc, const void *bias, U32 tmpBytes, void *tmp,
+    const TensorDesc *outputDesc, void *output, const ActivationParamSpec *activationDesc)
 {
-    return NOT_IMPLEMENTED;
+    (void)algorithm;
+    (void)scaleDesc;
+    (void)biasDesc;
+    if (inputDesc == nullptr || filterDesc == nullptr || outputDesc == nullptr || convParamSpec == nullptr) {
+        return NULL_POINTER;
+    }
+    if (is_bnn(filterDesc->dt)) {
+        // `scale` and `bias`: fp16 per-output-channel arrays (convolution.cpp:413-423 splits them)
+        return bnn_run(inputDesc, input, filterDesc, filter, convParamSpec, scale, bias, tmpBytes, tmp, outputDesc,
+            output);
+    }
+    return conv_i8_run(inputDesc, input, eltwiseInput, filterDesc, filter, convParamSpec, scale, bias, tmpBytes, tmp,
+        outputDesc, output, activationDesc);
 }
-}
+
+}  // extern "C"

@@ -21,20 +21,19 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace b200 {
 namespace {
 
-constexpr int BLOCK_M = 128;
-constexpr int BLOCK_K = 128;         // bytes of K per stage = one 128B swizzle row
+using namespace tc;
+
 constexpr int MAX_BLOCK_N = 256;
 constexpr int STAGES = 4;
-constexpr int UMMA_K = 32;           // K per tcgen05.mma.kind::i8
 constexpr int EPI_WARPS = 8;
 constexpr int EPI_THREADS = EPI_WARPS * 32;
 constexpr int NUM_THREADS = 64 + EPI_THREADS;
 constexpr uint32_t TMEM_COLS = 512;  // 2 accumulators x 256 columns
-constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // per wait; far above any legitimate wait
 
 constexpr int SMEM_A_STAGE = BLOCK_M * BLOCK_K;        // 16 KiB
 constexpr int SMEM_B_STAGE = MAX_BLOCK_N * BLOCK_K;    // 32 KiB
@@ -63,146 +62,6 @@ struct Params {
     int *status;
     int vec_ok;             // rows of C are 16-byte aligned -> vector stores allowed
 };
-
-// ---- PTX wrappers ----------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void *p)
-{
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait: false when the limit ran out (the caller then aborts the CTA's work).
-__device__ __forceinline__ uint64_t global_ns()
-{
-    uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
-{
-    if (mbar_try_wait(bar, parity)) {
-        return true;
-    }
-    const uint64_t t0 = global_ns();
-    for (;;) {
-        for (int i = 0; i < 64; ++i) {
-            if (mbar_try_wait(bar, parity)) {
-                return true;
-            }
-        }
-        if (global_ns() - t0 > WAIT_LIMIT_NS) {
-            return false;
-        }
-    }
-}
-__device__ __forceinline__ void tma_load_2d(const CUtensorMap *map, uint64_t *bar, void *dst, int x, int y)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
-        : "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_before()
-{
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_after()
-{
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tcgen05_commit(uint64_t *bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-    uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
-          "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
-          "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
-          "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-// The registers are listed as read-write operands so that no use of them can be scheduled above
-// the wait (tcgen05.ld delivers them asynchronously).
-__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32])
-{
-    asm volatile("tcgen05.wait::ld.sync.aligned;"
-                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
-                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
-                   "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
-                   "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
-                   "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
-                 :
-                 : "memory");
-}
-// usat8( rne(f) + 128 ) without a float->int conversion instruction: adding 1.5 * 2^23 rounds f to
-// an integer (nearest even) in the low mantissa bits; the integer subtraction removes the bias and
-// adds the zero point.  rne(f) in [-128, 127] maps to 0..255; every other input (large, negative
-// below -128, NaN, infinity) leaves a word above 255, which the unsigned clamp turns into 255 --
-// exactly what vcvtps2dq + vpaddd 128 + vpmovusdb store.
-__device__ __forceinline__ uint32_t f32_to_u8_zp128(float f)
-{
-    return min(__float_as_uint(__fadd_rn(f, 12582912.0f)) - (0x4B400000u - 128u), 255u);
-}
-
-// Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows of 128 bytes, groups of
-// 8 rows 1024 bytes apart (stride byte offset), descriptor version 1, layout type 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr)
-{
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)1 << 16;             // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t)(1024 >> 4) << 32;   // stride byte offset
-    d |= (uint64_t)1 << 46;             // version
-    d |= (uint64_t)2 << 61;             // SWIZZLE_128B
-    return d;
-}
-// Instruction descriptor of kind::i8: D = s32 (2 << 4), A = u8 (0 << 7), B = s8 (1 << 10), both
-// K-major, N >> 3 at bit 17, M >> 4 at bit 24; dense, no saturation.
-__device__ __forceinline__ uint32_t make_idesc_i8(uint32_t n)
-{
-    return (2u << 4) | (0u << 7) | (1u << 10) | ((n >> 3) << 17) | ((uint32_t)(BLOCK_M >> 4) << 24);
-}
 
 // ---- epilogue for 32 consecutive columns of one row: the common case ---------------------------
 // Full, 16-byte aligned chunk, C overwritten, one conversion factor per column.  Kept free of
@@ -658,18 +517,11 @@ EncodeTiledFn encode_fn()
 // out-of-range elements read as zero.
 bool make_map(CUtensorMap *map, const void *base, uint64_t inner, uint64_t rows, uint64_t pitch, uint32_t box_rows)
 {
-    EncodeTiledFn fn = encode_fn();
-    if (fn == nullptr) {
-        return false;
-    }
-    cuuint64_t dims[2] = {inner, rows};
-    cuuint64_t strides[1] = {pitch};
-    cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
-        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS;
+    const uint64_t dims[2] = {inner, rows};
+    const uint64_t strides[1] = {pitch};
+    const uint32_t box[2] = {(uint32_t)BLOCK_K, box_rows};
+    const uint32_t estr[2] = {1, 1};
+    return encode_tiled_u8(map, 2, base, dims, strides, box, estr, true);
 }
 
 // Tile width: the widest of 256 / 192 / 128 / 64 / 32 columns that still gives every SM a tile,
@@ -697,6 +549,34 @@ uint32_t pick_block_n(uint32_t M, uint32_t N, int sms)
 }
 
 }  // namespace
+
+bool tensor_map_encoder_available()
+{
+    return encode_fn() != nullptr;
+}
+
+bool encode_tiled_u8(void *map, uint32_t rank, const void *base, const uint64_t *dims, const uint64_t *strides,
+    const uint32_t *box, const uint32_t *elem_strides, bool swizzle128)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) {
+        return false;
+    }
+    cuuint64_t d[5], st[4];
+    cuuint32_t b[5], es[5];
+    for (uint32_t i = 0; i < rank; ++i) {
+        d[i] = dims[i];
+        b[i] = box[i];
+        es[i] = elem_strides[i];
+        if (i + 1 < rank) {
+            st[i] = strides[i];
+        }
+    }
+    CUresult r = fn(reinterpret_cast<CUtensorMap *>(map), CU_TENSOR_MAP_DATA_TYPE_UINT8, rank, const_cast<void *>(base), d,
+        st, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
 
 bool gemm_tcgen05_eligible(uint32_t M, uint32_t N, uint32_t K, const void *A, const void *B, uint32_t Kp,
     bool a_transposed)

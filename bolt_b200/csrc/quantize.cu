@@ -274,6 +274,33 @@ EE absmax_i32_host(const int32_t *d_x, uint64_t n, int *mx)
 }
 
 }  // namespace
+
+// int32 (device) -> u8 (device) with the reference's scale protocol; used by the convolution's
+// u8 output (convolution_direct.cpp:2798-2806).  scale2 is a host array of two floats.
+EE quantize_i32_u8_device(const int32_t *d_src, uint64_t n, uint8_t *d_q, F32 *scale2)
+{
+    DeviceCtx *c = ctx();
+    if (c == nullptr) {
+        return UNKNOWN;
+    }
+    float raw = 0;
+    if (scale2[0] < 0 && scale2[1] > 0) {
+        int mx = 0;
+        B200_EE(absmax_i32_host(d_src, n, &mx));
+        raw = (mx == 0) ? 1.0f : 127.0f / (float)mx;
+        scale2[0] = scale2[1] * raw;
+    } else if (scale2[0] > 0 && scale2[1] > 0) {
+        raw = scale2[0] / scale2[1];
+    }
+    if (n == 0) {
+        return SUCCESS;
+    }
+    to8_kernel<int32_t, I32ToU8><<<grid_for((n + 15) / 16, c->sm_count), TPB, 0, tls().stream>>>(d_src, n, d_q, I32ToU8{raw});
+    count_launch();
+    B200_CUDA(cudaGetLastError());
+    return SUCCESS;
+}
+
 }  // namespace b200
 
 using namespace b200;

@@ -292,3 +292,287 @@ void oracle_dequantize_u8_f32(const uint8_t *q, uint64_t n, float scale, float *
         out[i] = (float)((int32_t)q[i] - 128) * factor;
     }
 }
+
+/* ------------------------------------------------------------------------------ */
+/* int8 convolution                                                               */
+/* ------------------------------------------------------------------------------ */
+
+/* compute/tensor/src/convolution.cpp:28-145 (convolution_infer_output_size) */
+void oracle_conv_out_hw(const oracle_conv_shape *s, uint32_t *oh, uint32_t *ow)
+{
+    uint32_t fhd = (s->fh - 1) * s->dil_h + 1, fwd = (s->fw - 1) * s->dil_w + 1;
+    *oh = (s->ih + s->pad_t + s->pad_b - fhd) / s->stride_h + 1;
+    *ow = (s->iw + s->pad_l + s->pad_r - fwd) / s->stride_w + 1;
+}
+
+/* element offset of channel c, pixel (h, w) of image n in a channel-blocked tensor whose blocks
+ * are `blk` channels wide with one narrower tail block (avx512/convolution_direct.cpp:2766,
+ * simdOc = min(16, ocSize)); blk == 0 is plain NCHW */
+static size_t blocked_off(uint32_t n, uint32_t C, uint32_t H, uint32_t W, uint32_t blk, uint32_t c,
+    uint32_t h, uint32_t w)
+{
+    if (blk == 0) {
+        return (((size_t)n * C + c) * H + h) * W + w;
+    }
+    uint32_t b = c / blk;
+    uint32_t width = (C - b * blk < blk) ? (C - b * blk) : blk; /* tail block */
+    return ((size_t)n * C + (size_t)b * blk) * H * W + ((size_t)h * W + w) * width + (c - b * blk);
+}
+
+/* avx512/convolution_direct.cpp:2584-2809 and convolution_1x1_direct.cpp:2073-2327:
+ * scaleO = scaleI * scaleF (:2687); offsetC + round(bias * scaleO) (:2703-2707, quantize.cpp:259-266);
+ * padding value 128 (transform_functions_int8.h:41,67-79), i.e. padded taps cancel exactly;
+ * fp32 output: (float)acc * (1/scaleO), + eltwise, max(0) (:2133-2165);
+ * u8 output: ReLU on int32, then quantizeI32ToU8 with a dynamic scale over the whole tensor,
+ * scale[1] = scaleO * raw written back (:2798-2806). */
+void oracle_conv_int8(const oracle_conv_shape *s, const uint8_t *in, const int8_t *filter,
+    const float *bias, const float *eltwise, void *out, float *scale, int32_t *acc32)
+{
+    uint32_t oh, ow;
+    oracle_conv_out_hw(s, &oh, &ow);
+    float scaleO = scale[0] * scale[2];
+    float factor = 1 / scaleO;
+    size_t total = (size_t)s->n * s->oc * oh * ow;
+    int32_t *acc = acc32 ? acc32 : (int32_t *)malloc(total * sizeof(int32_t));
+    for (uint32_t n = 0; n < s->n; ++n) {
+        for (uint32_t o = 0; o < s->oc; ++o) {
+            int32_t b = 0;
+            if (bias != NULL) {
+                float p = bias[o] * scaleO;
+                b = (int32_t)roundf(p);
+            }
+            for (uint32_t y = 0; y < oh; ++y) {
+                for (uint32_t x = 0; x < ow; ++x) {
+                    int32_t a = b;
+                    for (uint32_t c = 0; c < s->ic; ++c) {
+                        for (uint32_t kh = 0; kh < s->fh; ++kh) {
+                            int32_t iy = (int32_t)(y * s->stride_h + kh * s->dil_h) - (int32_t)s->pad_t;
+                            if (iy < 0 || iy >= (int32_t)s->ih) {
+                                continue; /* pad: (128 - 128) * w */
+                            }
+                            for (uint32_t kw = 0; kw < s->fw; ++kw) {
+                                int32_t ix = (int32_t)(x * s->stride_w + kw * s->dil_w) - (int32_t)s->pad_l;
+                                if (ix < 0 || ix >= (int32_t)s->iw) {
+                                    continue;
+                                }
+                                int32_t xv = in[blocked_off(n, s->ic, s->ih, s->iw, s->cin_block, c,
+                                    (uint32_t)iy, (uint32_t)ix)];
+                                int32_t wv = filter[(((size_t)o * s->ic + c) * s->fh + kh) * s->fw + kw];
+                                a += (xv - 128) * wv;
+                            }
+                        }
+                    }
+                    size_t off = blocked_off(n, s->oc, oh, ow, s->cout_block, o, y, x);
+                    if (!s->out_u8) {
+                        float f = (float)a * factor;
+                        if (eltwise != NULL) {
+                            f = f + eltwise[off];
+                        }
+                        if (s->relu) {
+                            f = (f > 0) ? f : 0.0f; /* vmaxps(f, 0) */
+                        }
+                        ((float *)out)[off] = f;
+                        if (acc32) {
+                            acc[off] = a;
+                        }
+                    } else {
+                        if (s->relu && a < 0) {
+                            a = 0; /* vpmaxsd(acc, 0) */
+                        }
+                        acc[off] = a;
+                    }
+                }
+            }
+        }
+    }
+    if (s->out_u8) {
+        float sc[2] = {-1, scaleO};
+        oracle_quantize_i32_u8(acc, total, (uint8_t *)out, sc);
+        scale[1] = sc[0];
+    } else {
+        scale[1] = scaleO;
+    }
+    if (!acc32) {
+        free(acc);
+    }
+}
+
+/* ------------------------------------------------------------------------------ */
+/* 1-bit convolution (ARMv8.2 semantics; no x86 build exists, so this part of the  */
+/* oracle is pinned only by hand-checkable cases: "parity unpinned")              */
+/* ------------------------------------------------------------------------------ */
+
+float oracle_f16_to_f32(uint16_t h)
+{
+    uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+    uint32_t exp = (h >> 10) & 0x1Fu, man = h & 0x3FFu, bits;
+    if (exp == 0) {
+        if (man == 0) {
+            bits = sign;
+        } else {
+            int e = -1;
+            do {
+                man <<= 1;
+                ++e;
+            } while (!(man & 0x400u));
+            bits = sign | ((uint32_t)(127 - 15 - e) << 23) | ((man & 0x3FFu) << 13);
+        }
+    } else if (exp == 31) {
+        bits = sign | 0x7F800000u | (man << 13);
+    } else {
+        bits = sign | ((exp + 112) << 23) | (man << 13);
+    }
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+/* exact value v = mant * 2^e2 (mant may be any signed 128-bit integer) -> binary16, RNE */
+static uint16_t round_to_f16(__int128 mant, int e2)
+{
+    if (mant == 0) {
+        return 0;
+    }
+    uint16_t sign = 0;
+    if (mant < 0) {
+        sign = 0x8000u;
+        mant = -mant;
+    }
+    unsigned __int128 m = (unsigned __int128)mant;
+    int msb = 127;
+    while (!((m >> msb) & 1)) {
+        --msb;
+    }
+    int e = msb + e2; /* value in [2^e, 2^(e+1)) */
+    /* number of fraction bits kept: 10 for normals; subnormals keep down to 2^-24 */
+    int lsb_exp = (e < -14) ? -24 : e - 10; /* weight of the last kept bit */
+    int shift = lsb_exp - e2;               /* drop `shift` low bits of m */
+    unsigned __int128 q;
+    if (shift <= 0) {
+        q = m << (-shift);
+    } else if (shift > 127) {
+        q = 0;
+    } else {
+        unsigned __int128 rem = m & ((((unsigned __int128)1) << shift) - 1);
+        unsigned __int128 half = ((unsigned __int128)1) << (shift - 1);
+        q = m >> shift;
+        if (rem > half || (rem == half && (q & 1))) {
+            ++q;
+        }
+    }
+    /* q * 2^lsb_exp; renormalise if rounding carried */
+    if (e >= -14) {
+        if (q >> 11) {
+            q >>= 1;
+            ++e;
+        }
+        if (e > 15) {
+            return sign | 0x7C00u; /* overflow -> inf */
+        }
+        return sign | (uint16_t)((e + 15) << 10) | (uint16_t)(q & 0x3FFu);
+    }
+    /* subnormal (q may round up to the smallest normal, which this encoding handles) */
+    return sign | (uint16_t)q;
+}
+
+uint16_t oracle_f32_to_f16(float f)
+{
+    uint32_t b;
+    memcpy(&b, &f, 4);
+    uint32_t exp = (b >> 23) & 0xFF, man = b & 0x7FFFFFu;
+    uint16_t sign = (uint16_t)((b >> 16) & 0x8000u);
+    if (exp == 255) {
+        return sign | 0x7C00u | (man ? 0x200u : 0);
+    }
+    if (exp == 0 && man == 0) {
+        return sign;
+    }
+    __int128 m = (exp == 0) ? man : (man | 0x800000u);
+    int e2 = (exp == 0 ? 1 : (int)exp) - 127 - 23;
+    if (e2 < -200) {
+        return sign;
+    }
+    uint16_t r = round_to_f16(m, e2);
+    return (uint16_t)(r | sign);
+}
+
+/* scvtf / ucvtf to half precision: RNE (convolution_xnor_A76.cpp:300-312) */
+uint16_t oracle_i32_to_f16(int32_t v)
+{
+    return round_to_f16((__int128)v, 0);
+}
+
+/* finite binary16 -> integer multiple of 2^-24 */
+static int64_t f16_units(uint16_t h)
+{
+    int64_t man = h & 0x3FF;
+    int exp = (h >> 10) & 0x1F;
+    int64_t v = (exp == 0) ? man : ((man | 0x400) << (exp - 1));
+    return (h & 0x8000u) ? -v : v;
+}
+
+/* fmla in half precision: a * b + c with one rounding (convolution_xnor_A76.cpp:322-374).
+ * Finite inputs only (the convolution never produces anything else from finite scale/bias). */
+uint16_t oracle_f16_fma(uint16_t a, uint16_t b, uint16_t c)
+{
+    __int128 prod = (__int128)f16_units(a) * f16_units(b); /* units of 2^-48 */
+    __int128 sum = prod + ((__int128)f16_units(c) << 24);
+    if (sum == 0) {
+        /* exact zero: sign of +0 unless both addends are negative zeros */
+        int pneg = ((a ^ b) & 0x8000u) != 0, cneg = (c & 0x8000u) != 0;
+        return (pneg && cneg) ? 0x8000u : 0;
+    }
+    return round_to_f16(sum, -48);
+}
+
+/* B3 (common/uni/include/data_type.h:197-233): bit = (x >= 0) for DT_BIN11, (x >= 0.5) for DT_BIN01.
+ * B4 (cpu/arm/bnn/convolution_xnor_A76.cpp:67-79,300-374): zero-bit padding (= -1),
+ *    sum = fh*fw*ic - 2*popcount(x XOR w) in int16, out = fma_f16((f16)sum, scale, bias).
+ * B5 (cpu/arm/bnn/convolution_dorefa_A76.cpp:167-199,290-306): zero padding, sum = popcount(x AND w).
+ * Filter bits: NCHW, MSB first (cpu/general/convolution.cpp:161-179). Input / output: fp16 NCHWc8. */
+void oracle_bnn_conv(const oracle_bnn_shape *s, const uint16_t *in, const uint8_t *filter_bits,
+    const uint16_t *scale, const uint16_t *bias, uint16_t *out, int32_t *sum32)
+{
+    uint32_t oh = (s->ih + s->pad_t + s->pad_b - s->fh) / s->stride_h + 1;
+    uint32_t ow = (s->iw + s->pad_l + s->pad_r - s->fw) / s->stride_w + 1;
+    size_t npix = (size_t)s->n * s->ic * s->ih * s->iw;
+    uint8_t *xb = (uint8_t *)malloc(npix);
+    float thr = s->xnor ? 0.0f : 0.5f;
+    for (size_t i = 0; i < npix; ++i) {
+        xb[i] = oracle_f16_to_f32(in[i]) >= thr;
+    }
+    for (uint32_t n = 0; n < s->n; ++n) {
+        for (uint32_t o = 0; o < s->oc; ++o) {
+            for (uint32_t y = 0; y < oh; ++y) {
+                for (uint32_t x = 0; x < ow; ++x) {
+                    int32_t sum = 0;
+                    for (uint32_t c = 0; c < s->ic; ++c) {
+                        for (uint32_t kh = 0; kh < s->fh; ++kh) {
+                            for (uint32_t kw = 0; kw < s->fw; ++kw) {
+                                size_t fp = (((size_t)o * s->ic + c) * s->fh + kh) * s->fw + kw;
+                                int wbit = (filter_bits[fp / 8] >> (7 - fp % 8)) & 1;
+                                int32_t iy = (int32_t)(y * s->stride_h + kh) - (int32_t)s->pad_t;
+                                int32_t ix = (int32_t)(x * s->stride_w + kw) - (int32_t)s->pad_l;
+                                int xbit = 0; /* padding is a zero bit in both modes */
+                                if (iy >= 0 && iy < (int32_t)s->ih && ix >= 0 && ix < (int32_t)s->iw) {
+                                    xbit = xb[blocked_off(n, s->ic, s->ih, s->iw, 8, c, (uint32_t)iy, (uint32_t)ix)];
+                                }
+                                if (s->xnor) {
+                                    sum += (xbit == wbit) ? 1 : -1;
+                                } else {
+                                    sum += xbit & wbit;
+                                }
+                            }
+                        }
+                    }
+                    size_t off = blocked_off(n, s->oc, oh, ow, 8, o, y, x);
+                    if (sum32) {
+                        sum32[off] = sum;
+                    }
+                    out[off] = oracle_f16_fma(oracle_i32_to_f16((int16_t)sum), scale[o], bias[o]);
+                }
+            }
+        }
+    }
+    free(xb);
+}

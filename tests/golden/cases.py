@@ -52,3 +52,38 @@ def quant_inputs(i):
     b[0] = 0.5
     off = synth.integers(seed + 400, (n,), -1000, 1000)
     return x, a, u, b, off
+
+
+# (n, ic, ih, iw, oc, fh, fw, stride, pad)
+CONV_SHAPES = [(1, 16, 8, 8, 16, 1, 1, 1, 0), (2, 32, 9, 7, 48, 3, 3, 1, 1), (1, 64, 14, 14, 64, 3, 3, 2, 1),
+               (2, 16, 6, 6, 24, 1, 1, 2, 0), (1, 8, 5, 5, 8, 3, 3, 1, 1), (1, 24, 7, 7, 40, 3, 3, 1, 1),
+               (1, 64, 12, 12, 32, 1, 1, 1, 0), (1, 128, 9, 9, 32, 3, 3, 2, 1)]
+CONV_SCALES = [37.5, -1.0, 310.0]   # input scale, output scale (dynamic), filter scale
+
+
+def to_blocked(x, blk):
+    """[N, C, H, W] -> flat channel-blocked layout: blocks of `blk` channels, narrower tail block."""
+    n, c, h, w = x.shape
+    out = []
+    for i in range(n):
+        cb = 0
+        while cb < c:
+            wd = min(blk, c - cb)
+            out.append(x[i, cb:cb + wd].transpose(1, 2, 0).reshape(-1))
+            cb += wd
+    return np.concatenate(out)
+
+
+def conv_inputs(i, in_block):
+    n, ic, ih, iw, oc, fh, fw, st, pad = CONV_SHAPES[i]
+    x = synth.relu_u8(7000 + i, (n, ic, ih, iw))
+    w = synth.s8(7100 + i, (oc, ic, fh, fw))
+    bias = synth.normal(7200 + i, (oc,), 0.1)
+    return to_blocked(x, in_block), w, bias
+
+
+def conv_variants(i):
+    """(in_block, out_u8, relu) combinations pinned for shape i"""
+    ic = CONV_SHAPES[i][1]
+    blocks = (8, 16) if ic % 16 == 0 else (8,)
+    return [(b, u, r) for b in blocks for u in (0, 1) for r in (0, 1)]

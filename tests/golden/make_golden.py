@@ -87,11 +87,31 @@ def quant_outputs():
     return out
 
 
+def conv_outputs():
+    import ctypes as C
+    out = {}
+    for i, (n, ic, ih, iw, oc, fh, fw, st, pad) in enumerate(cases.CONV_SHAPES):
+        oh, ow = (ih + 2 * pad - fh) // st + 1, (iw + 2 * pad - fw) // st + 1
+        tot = n * oc * oh * ow
+        for blk, out_u8, relu in cases.conv_variants(i):
+            xin, w, bias = cases.conv_inputs(i, blk)
+            pl = O.ref.ref_conv_plan(n, ic, ih, iw, oc, fh, fw, st, pad, blk, 16, out_u8, relu, ptr(w))
+            assert pl
+            res = np.zeros(tot + 64, np.uint8 if out_u8 else np.float32)
+            sc = np.array(cases.CONV_SCALES, np.float32)
+            assert O.ref.ref_conv_run(pl, ptr(xin.copy()), None, ptr(bias), ptr(res), ptr(sc)) == 0
+            O.ref.ref_conv_free(pl)
+            key = "c%d_%d%d%d" % (i, blk, out_u8, relu)
+            out[key], out[key + "_scale"] = res[:tot].copy(), sc.copy()
+    return out
+
+
 def main():
+    np.savez_compressed(os.path.join(HERE, "conv.npz"), **conv_outputs())
     np.savez_compressed(os.path.join(HERE, "gemm.npz"), **gemm_outputs())
     np.savez_compressed(os.path.join(HERE, "gemv.npz"), **gemv_outputs())
     np.savez_compressed(os.path.join(HERE, "quantize.npz"), **quant_outputs())
-    for f in ("gemm.npz", "gemv.npz", "quantize.npz"):
+    for f in ("gemm.npz", "gemv.npz", "quantize.npz", "conv.npz"):
         print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
 
 

@@ -89,6 +89,20 @@ def test_golden_quantize():
         assert same_bits(r, g["q%d_biasoff" % i])
 
 
+def test_golden_conv():
+    import ctypes as C
+    g = np.load(os.path.join(GOLD, "conv.npz"))
+    for i, (n, ic, ih, iw, oc, fh, fw, st, pad) in enumerate(cases.CONV_SHAPES):
+        for blk, out_u8, relu in cases.conv_variants(i):
+            xin, w, bias = cases.conv_inputs(i, blk)
+            s = O.ConvShape(n, ic, ih, iw, oc, fh, fw, st, st, pad, pad, pad, pad, 1, 1, blk, 16, relu, out_u8)
+            key = "c%d_%d%d%d" % (i, blk, out_u8, relu)
+            out = np.zeros(g[key].size, g[key].dtype)
+            sc = np.array(cases.CONV_SCALES, np.float32)
+            O.port.oracle_conv_int8(C.byref(s), ptr(xin), ptr(w), ptr(bias), None, ptr(out), ptr(sc), None)
+            assert same_bits(out, g[key]) and same_bits(sc, g[key + "_scale"]), key
+
+
 def test_known_answers_u8_saturation():
     """The reference's u8 epilogue reads the rounded sum as unsigned: negatives store 255."""
     assert O.port.oracle_usat8(-800 + 128) == 255
