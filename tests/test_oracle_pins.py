@@ -103,6 +103,37 @@ def test_golden_conv():
             assert same_bits(out, g[key]) and same_bits(sc, g[key + "_scale"]), key
 
 
+def test_bnn_oracle_hand_checkable_cases():
+    """The 1-bit path has no runnable reference here ("parity unpinned"): anchor the restatement on
+    cases whose answers follow directly from the definitions in
+    cpu/arm/bnn/convolution_xnor_A76.cpp:67-79,300-374 and convolution_dorefa_A76.cpp:167-199."""
+    import ctypes as C
+    f16 = lambda v: int(np.float16(v).view(np.uint16))
+    n, ic, hw, oc = 1, 8, 3, 8
+    ones_w = np.full(oc * ic * 9 // 8, 0xFF, np.uint8)                  # every weight bit set (+1)
+    x_pos = np.full(ic * hw * hw, f16(1.0), np.uint16)                   # every activation bit set
+    scale, bias = np.full(oc, f16(0.5), np.uint16), np.full(oc, f16(0.25), np.uint16)
+    out, sums = np.zeros(oc * hw * hw, np.uint16), np.zeros(oc * hw * hw, np.int32)
+    s = O.BnnShape(n, ic, hw, hw, oc, 3, 3, 1, 1, 1, 1, 1, 1, 1)
+    O.port.oracle_bnn_conv(C.byref(s), ptr(x_pos), ptr(ones_w), ptr(scale), ptr(bias), ptr(out), ptr(sums))
+    sums = sums.reshape(oc // 8, hw, hw, 8)
+    # XNOR: valid taps contribute +ic each, padded taps (-1 against +1) contribute -ic each
+    assert sums[0, 1, 1, 0] == 9 * ic and sums[0, 0, 0, 0] == 4 * ic - 5 * ic and sums[0, 0, 1, 0] == 6 * ic - 3 * ic
+    assert out.reshape(oc // 8, hw, hw, 8)[0, 1, 1, 0] == f16(72 * 0.5 + 0.25)
+    s = O.BnnShape(n, ic, hw, hw, oc, 3, 3, 1, 1, 1, 1, 1, 1, 0)
+    O.port.oracle_bnn_conv(C.byref(s), ptr(x_pos), ptr(ones_w), ptr(scale), ptr(bias), ptr(out), ptr(sums))
+    sums = sums.reshape(oc // 8, hw, hw, 8)
+    # DoReFa: popcount(and), padding contributes nothing
+    assert sums[0, 1, 1, 0] == 9 * ic and sums[0, 0, 0, 0] == 4 * ic and sums[0, 0, 1, 0] == 6 * ic
+    x_thr = np.full(ic * hw * hw, f16(0.49), np.uint16)                  # below 0.5 -> bit 0 in DoReFa, bit 1 in XNOR
+    O.port.oracle_bnn_conv(C.byref(s), ptr(x_thr), ptr(ones_w), ptr(scale), ptr(bias), ptr(out), ptr(sums))
+    assert not sums.any()
+    # fp16 fused multiply-add: one rounding (2049 * 1 + 1 = 2050 exactly; two roundings would give 2048 + 1 -> 2048)
+    assert O.port.oracle_f16_fma(f16(2048.0), f16(1.0), f16(1.0)) == f16(2048.0)      # 2049 ties to even 2048
+    assert O.port.oracle_f16_fma(f16(1.0009765625), f16(1.0009765625), f16(-1.0)) == int(np.float16(0.001953125 + 2.0 ** -20).view(np.uint16))
+    assert O.port.oracle_i32_to_f16(2049) == f16(2048.0) and O.port.oracle_i32_to_f16(2051) == f16(2052.0)
+
+
 def test_known_answers_u8_saturation():
     """The reference's u8 epilogue reads the rounded sum as unsigned: negatives store 255."""
     assert O.port.oracle_usat8(-800 + 128) == 255
