@@ -27,6 +27,7 @@ DT_BIN01, DT_BIN11, DT_F32_8Q, DT_U8_Q = 7, 8, 9, 10
 DF_NCHW, DF_NCHWC8, DF_NCHWN16C8, DF_TRANSPOSE, DF_NORMAL = 0, 2, 9, 13, 14
 DF_NK, DF_NKN32K4, DF_NKNxKx, DF_NCHWC16, DF_NCHWC2NxC4 = 17, 21, 39, 41, 42
 ACTIVATION_NULL, ACTIVATION_RELU = 0, 1
+NOALLOC_MAX_ELEMENTS = 67108864  # BOLT_B200_NOALLOC_MAX_ELEMENTS
 CONVOLUTION_ALGORITHM_POINTWISE, CONVOLUTION_ALGORITHM_DIRECT = 0, 1
 CONVOLUTION_ALGORITHM_BNN, CONVOLUTION_ALGORITHM_NULL = 6, 9
 
@@ -128,6 +129,7 @@ SIGNATURES = {
     "quantize_bias_offsetC_cuda_b200": (C.c_int, [_vp, _TDp, _u32, _vp, _TDp, _f32p, _vp]),
     "dequantize_cuda_b200": (C.c_int, [_TDp, _vp, _f32p, _TDp, _vp, _TDp, _vp]),
     "bolt_b200_absmax_scale_f32": (C.c_int, [_vp, C.c_uint64, _vp]),
+    "bolt_b200_quantize_f32_u8_noalloc": (C.c_int, [_vp, C.c_uint64, _vp, _vp]),
     "convolution_infer_forward_algorithm_cuda_b200": (
         C.c_int, [_TDp, _TDp, _TDp, C.POINTER(ConvolutionParamSpec), _u32, _u32p, _u32]),
     "convolution_transform_filter_bytes_cuda_b200": (

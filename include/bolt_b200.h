@@ -291,6 +291,21 @@ EE dequantize_cuda_b200(const TensorDesc *qDesc, const void *qData, const F32 *s
  * pipelines that stay on the stream.  d_scale: one float on the device. */
 EE bolt_b200_absmax_scale_f32(const F32 *data, uint64_t n, F32 *d_scale);
 
+/* No counterpart in Bolt.  F32 -> U8_Q with a dynamic per-tensor scale (the arithmetic of
+ * quantize_cuda_b200) for callers that must not allocate device memory when they call: servers
+ * whose own pool owns the whole GPU, hosts that forbid allocation on the serving path, fixed
+ * memory budgets.  It makes no cudaMalloc / cudaFree call and does not create the library's
+ * per-device context; its reduction scratch is a fixed 16.5 KiB array inside the library's device
+ * image (held by every GPU that loads the library until the process exits), which limits one call
+ * to BOLT_B200_NOALLOC_MAX_ELEMENTS elements -- more returns NOT_SUPPORTED, as does n == 0.
+ * data, q and d_scale (one float, receives 127/absmax) are device pointers; the work is enqueued
+ * on the thread's current stream (bolt_b200_set_stream) of the current CUDA device.  The first
+ * call on a device looks up the scratch address; make that call before any stream capture.  All
+ * calls share the one array: two calls that overlap on the GPU (different streams or threads)
+ * race and may both produce wrong scales -- serialise them. */
+#define BOLT_B200_NOALLOC_MAX_ELEMENTS 67108864ull
+EE bolt_b200_quantize_f32_u8_noalloc(const F32 *data, uint64_t n, UINT8 *q, F32 *d_scale);
+
 /* ---- int8 and 1-bit convolution --------------------------------------------------------------- */
 
 /* replaces compute/tensor/src/cpu/x86/convolution.cpp:23-103 */
