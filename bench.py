@@ -309,6 +309,23 @@ def run_b200_arm(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_side_workload(args):
+    """The kernels next to the headline (bolt_b200/workloads.py), one JSON line."""
+    import torch
+
+    import bolt_b200 as B
+    from bolt_b200 import workloads
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; there is no CPU fallback")
+    B.load(build_if_missing=False)
+    peaks, src = measured_peaks()
+    res = workloads.WORKLOADS[args.workload](peaks)
+    res["peaks"] = {"hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"], "source": src}
+    res["device_status"] = B.lib().bolt_b200_device_status()
+    print(json.dumps(res))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -316,11 +333,18 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU leg (profiling runs)")
+    ap.add_argument("--workload", default="bert_stack",
+                    help="bert_stack (the headline, default) or one of the side workloads: ffn, gemv, quantize, "
+                         "resnet_conv, bnn (1 GPU, prints that workload's figures as one JSON line)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.workload != "bert_stack":
+        if rank == 0:
+            run_side_workload(args)
+        return
     if args.impl == "reference":
         run_reference_arm(args, rank)
     else:

@@ -1,0 +1,257 @@
+"""Synthetic workloads for the kernels next to the headline GEMM stack: the FFN-shaped GEMM sweep
+and GEMV (BASELINE config 4), the ResNet-50-shaped int8 convolutions (config 3), the 1-bit
+convolution (config 5) and stand-alone quantize / dequantize.  Each returns a dict of measured
+figures; `bench.py --workload NAME` prints it as one JSON line.
+
+Timing: CUDA events on the launching stream, one pair per iteration, a 256 MiB write between
+iterations so that nothing is served from L2 by accident, 3 warm-up iterations.
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import (CHECK_STATUS, CONVOLUTION_ALGORITHM_NULL, DF_NCHW, DF_NCHWC8, DF_NCHWC16, DF_NORMAL, DT_BIN11, DT_F16,
+               DT_F32, DT_I8, DT_I32, DT_U8_Q, GemmEpilogue, conv_param, convolution, convolution_infer_forward_algorithm,
+               convolution_infer_forward_tmp_bytes, convolution_infer_output_size, convolution_transform_filter,
+               convolution_transform_filter_bytes, lib, matrix_matrix_multiply_transform_rhs,
+               matrix_matrix_multiply_transform_rhs_bytes, synth, tensor1d, tensor2df, tensor4df)
+
+
+def _torch():
+    import torch
+
+    return torch
+
+
+def _p(t, off=0):
+    return C.c_void_p(t.data_ptr() + off)
+
+
+class Timer:
+    def __init__(self):
+        torch = _torch()
+        self.torch = torch
+        self.flush = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def graph(self, fn):
+        """capture fn() (stream-only work) into a CUDA graph on a side stream; returns the replay callable"""
+        torch = self.torch
+        fn()
+        torch.cuda.synchronize()
+        st = torch.cuda.Stream()
+        lib().bolt_b200_set_stream(C.c_void_p(st.cuda_stream))
+        g = torch.cuda.CUDAGraph()
+        try:
+            with torch.cuda.graph(g, stream=st):
+                fn()
+        finally:
+            lib().bolt_b200_set_stream(None)
+        return g.replay
+
+    def run(self, fn, iters=10, warmup=3):
+        """mean milliseconds per call of fn()"""
+        torch = self.torch
+        for _ in range(warmup):
+            self.flush.fill_(1)
+            fn()
+        evs = []
+        for _ in range(iters):
+            self.flush.fill_(1)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            evs.append((a, b))
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in evs) / iters
+
+
+def _dev(a):
+    torch = _torch()
+    return torch.from_numpy(np.ascontiguousarray(a).view(np.uint8).reshape(-1).copy()).cuda()
+
+
+def _packed_weight(K, N, seed):
+    """random s8 [K, N] generated on the device (the values do not matter for speed), packed"""
+    torch = _torch()
+    w = torch.randint(-127, 128, (K, N), dtype=torch.int8, device="cuda", generator=torch.Generator("cuda").manual_seed(seed))
+    desc = tensor2df(DT_I8, DF_NORMAL, K, N)
+    nbytes, rhs = matrix_matrix_multiply_transform_rhs_bytes(desc)
+    packed = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    matrix_matrix_multiply_transform_rhs(desc, _p(w), _p(packed))
+    torch.cuda.synchronize()
+    return packed, rhs
+
+
+def ffn_sweep(peaks, iters=5):
+    """u8 x s8 GEMM, K 8192, N 28672, M in {16, 128, 2048, 16384}, fused u8 output."""
+    torch = _torch()
+    L, tm = lib(), Timer()
+    K, N = 8192, 28672
+    packed, rhs = _packed_weight(K, N, 1)
+    L.bolt_b200_set_pointer_mode(1)
+    rows = []
+    for M in (16, 128, 2048, 16384):
+        a = torch.randint(0, 256, (M, K), dtype=torch.uint8, device="cuda")
+        c = torch.empty(M * N, dtype=torch.uint8, device="cuda")
+        ep = GemmEpilogue()
+        ep.out_dt, ep.accumulate, ep.out_scale, ep.sA, ep.sB = DT_U8_Q, 0, 0.002, 1.0, 1.0
+        ms = tm.run(lambda: L.bolt_b200_gemm_u8s8_ex(N, M, K, _p(a), _p(packed), _p(packed, rhs), _p(c), C.byref(ep)), iters)
+        ops = 2.0 * M * N * K
+        rows.append({"M": M, "ms": ms, "tops": ops / ms / 1e9, "weight_GBps": K * N / ms / 1e6})
+    L.bolt_b200_set_pointer_mode(0)
+    peak = 2.0 * peaks["bf16_tflops_sustained"]
+    best = max(rows, key=lambda r: r["tops"])
+    return {"workload": "ffn_gemm_sweep K=8192 N=28672", "rows": rows, "best_tops": best["tops"],
+            "frac_of_2x_bf16_sustained": best["tops"] / peak, "frac_of_nominal_4500": best["tops"] / 4500.0}
+
+
+def gemv(peaks, iters=20):
+    """M = 1: y = W x, W s8 [28672, 8192] pre-packed, x u8, int32 / fp32 / u8 outputs."""
+    torch = _torch()
+    from . import (DF_NKN32K4, matrix_vector_multiply_transform_weight, matrix_vector_multiply_transform_weight_bytes)
+
+    L, tm = lib(), Timer()
+    N, K = 28672, 8192
+    w = torch.randint(-127, 128, (N, K), dtype=torch.int8, device="cuda")
+    desc = tensor2df(DT_I8, DF_NORMAL, N, K)
+    nb = matrix_vector_multiply_transform_weight_bytes(desc)
+    packed = torch.zeros(nb, dtype=torch.uint8, device="cuda")
+    matrix_vector_multiply_transform_weight(desc, _p(w), _p(packed))
+    torch.cuda.synchronize()
+    del w
+    x = torch.randint(0, 256, (K,), dtype=torch.uint8, device="cuda")
+    y = torch.zeros(N, dtype=torch.int32, device="cuda")
+    off = ((N + 15) // 16 * 16) * ((K + 7) // 8 * 8)
+    L.bolt_b200_set_pointer_mode(1)
+    scale = (C.c_float * 2)(-1.0, 0.001)
+    out = {}
+    for name, sp in (("s32", None), ("u8", C.cast(scale, C.POINTER(C.c_float)))):
+        ms = tm.run(lambda: CHECK_STATUS(L.mvm_cuda_b200(N, K, DT_I8, DF_NKN32K4, _p(packed), _p(x), _p(y), _p(packed, off), sp)), iters)
+        bytes_ = N * K + K + 4 * N + (4 * N * 2 if sp is None else N)
+        out[name] = {"us": ms * 1e3, "GBps": bytes_ / ms / 1e6, "frac_of_hbm": bytes_ / ms / 1e6 / peaks["hbm_gbs"]}
+    L.bolt_b200_set_pointer_mode(0)
+    return {"workload": "gemv N=28672 K=8192", **out}
+
+
+def quantize(peaks, iters=20):
+    """stand-alone quantize / requantize / dequantize on a 4096 x 3072 tensor (config-2 activation)."""
+    torch = _torch()
+    L, tm = lib(), Timer()
+    n = 4096 * 3072
+    x = torch.randn(n, device="cuda")
+    acc = torch.randint(-100000, 100000, (n,), dtype=torch.int32, device="cuda")
+    q = torch.empty(n, dtype=torch.uint8, device="cuda")
+    f = torch.empty(n, dtype=torch.float32, device="cuda")
+    ds = torch.zeros(4, dtype=torch.float32, device="cuda")
+    hbm = peaks["hbm_gbs"]
+    res = {}
+
+    def dyn():
+        L.bolt_b200_absmax_scale_f32(_p(x), n, _p(ds))
+        L.bolt_b200_quantize_f32_u8_dev(_p(x), n, _p(q), _p(ds))
+
+    ms = tm.run(dyn, iters)
+    res["f32_to_u8_dynamic"] = {"us": ms * 1e3, "GBps_5B_per_elem": 5.0 * n / ms / 1e6, "GBps_9B_per_elem": 9.0 * n / ms / 1e6,
+                                "frac_of_hbm_9B": 9.0 * n / ms / 1e6 / hbm}
+    ms = tm.run(lambda: L.bolt_b200_quantize_f32_u8_dev(_p(x), n, _p(q), _p(ds)), iters)
+    res["f32_to_u8_given_scale"] = {"us": ms * 1e3, "GBps": 5.0 * n / ms / 1e6, "frac_of_hbm": 5.0 * n / ms / 1e6 / hbm}
+    L.bolt_b200_set_pointer_mode(1)
+    qd, dd = tensor1d(DT_I32, n), tensor1d(DT_F32, n)
+    bd = tensor1d(DT_F32, 0)
+    sc = (C.c_float * 1)(0.37)
+    ms = tm.run(lambda: L.dequantize_cuda_b200(C.byref(qd), _p(acc), C.cast(sc, C.POINTER(C.c_float)), C.byref(bd), None,
+                                               C.byref(dd), _p(f)), iters)
+    res["i32_to_f32"] = {"us": ms * 1e3, "GBps": 8.0 * n / ms / 1e6, "frac_of_hbm": 8.0 * n / ms / 1e6 / hbm}
+    L.bolt_b200_set_pointer_mode(0)
+    return {"workload": "quantize 4096x3072", **res}
+
+
+# (ic, hw, oc, k, stride, pad): the 22 distinct ResNet-50 layer shapes after the stem
+RESNET50_LAYERS = [
+    (64, 56, 64, 1, 1, 0), (64, 56, 64, 3, 1, 1), (64, 56, 256, 1, 1, 0), (256, 56, 64, 1, 1, 0), (256, 56, 128, 1, 1, 0),
+    (128, 56, 128, 3, 2, 1), (256, 56, 512, 1, 2, 0),
+    (128, 28, 128, 3, 1, 1), (128, 28, 512, 1, 1, 0), (512, 28, 128, 1, 1, 0), (512, 28, 256, 1, 1, 0),
+    (256, 28, 256, 3, 2, 1), (512, 28, 1024, 1, 2, 0),
+    (256, 14, 256, 3, 1, 1), (256, 14, 1024, 1, 1, 0), (1024, 14, 256, 1, 1, 0), (1024, 14, 512, 1, 1, 0),
+    (512, 14, 512, 3, 2, 1), (1024, 14, 2048, 1, 2, 0),
+    (512, 7, 512, 3, 1, 1), (512, 7, 2048, 1, 1, 0), (2048, 7, 512, 1, 1, 0)]
+
+
+def resnet_conv(peaks, batch=64, iters=5, out_u8=False):
+    """int8 convolution, NCHWc16 u8 input, ReLU, fused bias; fp32 output (or dynamic u8 requantize)."""
+    torch = _torch()
+    L, tm = lib(), Timer()
+    rows, tot_ops, tot_ms = [], 0.0, 0.0
+    target = DT_U8_Q if out_u8 else DT_F32
+    for (ic, hw, oc, k, st, pad) in RESNET50_LAYERS:
+        p = conv_param(oc, k, k, st, pad, 1, True)
+        in_desc = tensor4df(DT_U8_Q, DF_NCHWC16, batch, ic, hw, hw)
+        f_desc = tensor4df(DT_I8, DF_NCHW, oc, ic, k, k)
+        out_desc = convolution_infer_output_size(in_desc, f_desc, p, target)
+        oh = out_desc.dims[1]
+        alg = convolution_infer_forward_algorithm(in_desc, f_desc, out_desc, p, target)
+        w = torch.randint(-127, 128, (oc * ic * k * k,), dtype=torch.int8, device="cuda")
+        ftm = torch.zeros(convolution_transform_filter_bytes(f_desc, p, alg), dtype=torch.uint8, device="cuda")
+        ftm_desc = convolution_transform_filter(f_desc, _p(w), p, alg, _p(ftm))
+        tb = convolution_infer_forward_tmp_bytes(in_desc, ftm_desc, out_desc, p, alg)
+        x = torch.randint(128, 256, (batch * ic * hw * hw,), dtype=torch.uint8, device="cuda")
+        bias = torch.randn(oc, device="cuda") * 0.1
+        tmp = torch.empty(tb, dtype=torch.uint8, device="cuda")
+        out = torch.empty(batch * oc * oh * oh * (1 if out_u8 else 4), dtype=torch.uint8, device="cuda")
+        sc = [31.75, -1.0, 635.0]
+        L.bolt_b200_set_pointer_mode(1)
+
+        def call():
+            convolution(in_desc, _p(x), ftm_desc, _p(ftm), p, alg, list(sc), _p(bias), tb, _p(tmp), out_desc, _p(out), True)
+
+        fn = call
+        if not out_u8:  # the fp32 path never leaves the stream: replay it as a CUDA graph (no host time inside)
+            fn = tm.graph(call)
+        ms = tm.run(fn, iters)
+        L.bolt_b200_set_pointer_mode(0)
+        ops = 2.0 * batch * oc * oh * oh * ic * k * k
+        rows.append({"layer": "%dx%d %d->%d @%d s%d" % (k, k, ic, oc, hw, st), "ms": ms, "tops": ops / ms / 1e9})
+        tot_ops += ops
+        tot_ms += ms
+        del w, ftm, x, tmp, out
+        torch.cuda.empty_cache()
+    peak = 2.0 * peaks["bf16_tflops"]
+    return {"workload": "resnet50_int8_conv batch %d (%s out)" % (batch, "u8" if out_u8 else "fp32"), "rows": rows,
+            "total_ms": tot_ms, "tops": tot_ops / tot_ms / 1e9, "frac_of_2x_bf16": tot_ops / tot_ms / 1e9 / peak,
+            "note": "each call includes the bias/offset kernel and, for padded layers, the pad+relayout pass"}
+
+
+def bnn(peaks, batch=128, iters=5):
+    """1-bit 3x3 convolution, C 256 -> 256, 28 x 28, pad 1, XNOR mode, fp16 NCHWc8 in and out."""
+    torch = _torch()
+    L, tm = lib(), Timer()
+    ic = oc = 256
+    hw, k = 28, 3
+    p = conv_param(oc, k, k, 1, 1)
+    in_desc = tensor4df(DT_F16, DF_NCHWC8, batch, ic, hw, hw)
+    f_desc = tensor4df(DT_BIN11, DF_NCHW, oc, ic, k, k)
+    out_desc = tensor4df(DT_F16, DF_NCHWC8, batch, oc, hw, hw)
+    alg = convolution_infer_forward_algorithm(in_desc, f_desc, out_desc, p, DT_F16)
+    wbits = torch.randint(0, 256, (oc * ic * k * k // 8,), dtype=torch.uint8, device="cuda")
+    ftm = torch.zeros(convolution_transform_filter_bytes(f_desc, p, alg), dtype=torch.uint8, device="cuda")
+    ftm_desc = convolution_transform_filter(f_desc, _p(wbits), p, alg, _p(ftm))
+    tb = convolution_infer_forward_tmp_bytes(in_desc, ftm_desc, out_desc, p, alg)
+    x = torch.randn(batch * ic * hw * hw, device="cuda").half()
+    alpha = (torch.rand(oc, device="cuda") * 0.1 + 0.01).half()
+    beta = torch.zeros(oc, device="cuda").half()
+    tmp = torch.empty(tb, dtype=torch.uint8, device="cuda")
+    out = torch.empty(batch * oc * hw * hw, dtype=torch.float16, device="cuda")
+    L.bolt_b200_set_pointer_mode(1)
+    ms = tm.run(lambda: convolution(in_desc, _p(x), ftm_desc, _p(ftm), p, alg, _p(alpha), _p(beta), tb, _p(tmp), out_desc, _p(out)),
+                iters)
+    L.bolt_b200_set_pointer_mode(0)
+    words = batch * hw * hw * oc * (k * k * ic // 32)
+    bytes_ = x.numel() * 2 + out.numel() * 2 + oc * ic * k * k // 8
+    return {"workload": "bnn_xnor 3x3 C256 28x28 batch %d" % batch, "ms": ms, "Gword_ops_per_s": words / ms / 1e6,
+            "frac_of_popc_issue_4450G": words / ms / 1e6 / 4450.0, "GBps": bytes_ / ms / 1e6,
+            "frac_of_hbm": bytes_ / ms / 1e6 / peaks["hbm_gbs"],
+            "note": "bound by the popcount rate (16 per clock per SM, 4.45 T/s measured), not by HBM"}
+
+
+WORKLOADS = {"ffn": ffn_sweep, "gemv": gemv, "quantize": quantize, "resnet_conv": resnet_conv, "bnn": bnn}
