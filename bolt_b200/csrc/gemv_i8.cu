@@ -44,8 +44,15 @@ gemv_s8u8_kernel(uint32_t N, uint32_t K, const int8_t *__restrict__ W, uint32_t 
 {
     extern __shared__ __align__(16) uint8_t sx[];
     // stage x, zero padded to Kp (the packed weight is zero there, any value would do)
-    for (uint32_t k = threadIdx.x; k < Kp; k += blockDim.x) {
-        sx[k] = (k < K) ? x[k] : (uint8_t)0;
+    if ((K & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        for (uint32_t k = threadIdx.x * 16; k < Kp; k += blockDim.x * 16) {
+            *reinterpret_cast<uint4 *>(sx + k) =
+                (k < K) ? *reinterpret_cast<const uint4 *>(x + k) : make_uint4(0, 0, 0, 0);
+        }
+    } else {
+        for (uint32_t k = threadIdx.x; k < Kp; k += blockDim.x) {
+            sx[k] = (k < K) ? x[k] : (uint8_t)0;
+        }
     }
     __syncthreads();
     const uint32_t lane = threadIdx.x & 31;
@@ -140,8 +147,9 @@ EE launch_gemv(uint32_t N, uint32_t K, const int8_t *W, uint32_t Kp, const uint8
     B200_CUDA(err);
     const int vec_ok = (Kp % 16 == 0) && (reinterpret_cast<uintptr_t>(W) % 16 == 0);
     uint32_t blocks = (N + WARPS - 1) / WARPS;
-    // enough CTAs to fill the machine several times over, few enough that x is not re-staged too often
-    const uint32_t cap = (uint32_t)c->sm_count * 16;
+    // persistent-style grid: every CTA stages x once and then streams many rows (a short-lived CTA
+    // spends as long staging x as reading its rows)
+    const uint32_t cap = (uint32_t)c->sm_count * 4;
     if (blocks > cap) {
         blocks = cap;
     }

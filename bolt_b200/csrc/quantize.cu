@@ -13,7 +13,7 @@ constexpr int TPB = 256;
 inline uint32_t grid_for(uint64_t n_vec, int sms)
 {
     uint64_t blocks = (n_vec + TPB - 1) / TPB;
-    const uint64_t cap = (uint64_t)sms * 8;
+    const uint64_t cap = (uint64_t)sms * 16;
     if (blocks > cap) {
         blocks = cap;
     }

@@ -3,8 +3,9 @@ and GEMV (BASELINE config 4), the ResNet-50-shaped int8 convolutions (config 3),
 convolution (config 5) and stand-alone quantize / dequantize.  Each returns a dict of measured
 figures; `bench.py --workload NAME` prints it as one JSON line.
 
-Timing: CUDA events on the launching stream, one pair per iteration, a 256 MiB write between
-iterations so that nothing is served from L2 by accident, 3 warm-up iterations.
+Timing: CUDA events on the launching stream, one pair per iteration, a 256 MiB read between
+iterations (a read, so that L2 holds neither the workload's lines nor dirty lines whose write-back
+would compete with the timed kernel), 3 warm-up iterations.
 """
 import ctypes as C
 
@@ -33,6 +34,9 @@ class Timer:
         self.torch = torch
         self.flush = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")
 
+    def evict(self):
+        self.sink = self.flush.sum()
+
     def graph(self, fn):
         """capture fn() (stream-only work) into a CUDA graph on a side stream; returns the replay callable"""
         torch = self.torch
@@ -52,11 +56,11 @@ class Timer:
         """mean milliseconds per call of fn()"""
         torch = self.torch
         for _ in range(warmup):
-            self.flush.fill_(1)
+            self.evict()
             fn()
         evs = []
         for _ in range(iters):
-            self.flush.fill_(1)
+            self.evict()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             fn()
@@ -135,10 +139,11 @@ def gemv(peaks, iters=20):
 
 
 def quantize(peaks, iters=20):
-    """stand-alone quantize / requantize / dequantize on a 4096 x 3072 tensor (config-2 activation)."""
+    """stand-alone quantize / requantize / dequantize on a 16384 x 3072 tensor (four config-2
+    activations: 201 MB of fp32, larger than L2)."""
     torch = _torch()
     L, tm = lib(), Timer()
-    n = 4096 * 3072
+    n = 16384 * 3072
     x = torch.randn(n, device="cuda")
     acc = torch.randint(-100000, 100000, (n,), dtype=torch.int32, device="cuda")
     q = torch.empty(n, dtype=torch.uint8, device="cuda")
@@ -164,7 +169,7 @@ def quantize(peaks, iters=20):
                                                C.byref(dd), _p(f)), iters)
     res["i32_to_f32"] = {"us": ms * 1e3, "GBps": 8.0 * n / ms / 1e6, "frac_of_hbm": 8.0 * n / ms / 1e6 / hbm}
     L.bolt_b200_set_pointer_mode(0)
-    return {"workload": "quantize 4096x3072", **res}
+    return {"workload": "quantize 16384x3072", **res}
 
 
 # (ic, hw, oc, k, stride, pad): the 22 distinct ResNet-50 layer shapes after the stem
