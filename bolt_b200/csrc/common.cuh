@@ -140,7 +140,7 @@ EE cuda_ee(cudaError_t e);
 // rank <= 5; zero fill out of range.  `map` points at a CUtensorMap.
 bool tensor_map_encoder_available();
 bool encode_tiled_u8(void *map, uint32_t rank, const void *base, const uint64_t *dims, const uint64_t *strides,
-    const uint32_t *box, const uint32_t *elem_strides, bool swizzle128);
+    const uint32_t *box, const uint32_t *elem_strides, int swizzle_bytes /* 0, 64 or 128 */);
 
 // ---- kernel launchers (device pointers only) ----------------------------------------------
 struct GemmEpilogue {

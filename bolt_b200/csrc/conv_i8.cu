@@ -587,7 +587,7 @@ EE launch_conv_tcgen05(const uint8_t *xp, const int8_t *w, const int32_t *offs, 
         const uint64_t strides[4] = {16, (uint64_t)Wp * 16, (uint64_t)Hp * Wp * 16, (uint64_t)ICb * Hp * Wp * 16};
         const uint32_t box[5] = {16, p.TW * sW, p.TH * sH, p.G, 1};
         const uint32_t es[5] = {1, sW, sH, 1, 1};
-        if (!encode_tiled_u8(&map_x, 5, xp, dims, strides, box, es, false)) {
+        if (!encode_tiled_u8(&map_x, 5, xp, dims, strides, box, es, 0)) {
             return NOT_SUPPORTED;
         }
     }
@@ -597,7 +597,7 @@ EE launch_conv_tcgen05(const uint8_t *xp, const int8_t *w, const int32_t *offs, 
         const uint64_t strides[1] = {K};
         const uint32_t box[2] = {(uint32_t)BLOCK_K, p.block_n};
         const uint32_t es[2] = {1, 1};
-        if (!encode_tiled_u8(&map_w, 2, w, dims, strides, box, es, true)) {
+        if (!encode_tiled_u8(&map_w, 2, w, dims, strides, box, es, 128)) {
             return NOT_SUPPORTED;
         }
     }

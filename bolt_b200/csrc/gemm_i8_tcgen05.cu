@@ -29,18 +29,17 @@ namespace {
 using namespace tc;
 
 constexpr int MAX_BLOCK_N = 256;
-constexpr int STAGES = 4;
+constexpr int MAX_STAGES = 8;        // the ring is as deep as shared memory allows for the tile width
 constexpr int EPI_WARPS = 8;
 constexpr int EPI_THREADS = EPI_WARPS * 32;
 constexpr int NUM_THREADS = 64 + EPI_THREADS;
 constexpr uint32_t TMEM_COLS = 512;  // 2 accumulators x 256 columns
 
 constexpr int SMEM_A_STAGE = BLOCK_M * BLOCK_K;        // 16 KiB
-constexpr int SMEM_B_STAGE = MAX_BLOCK_N * BLOCK_K;    // 32 KiB
 
 struct __align__(16) SmemCtl {
-    uint64_t full[STAGES];
-    uint64_t empty[STAGES];
+    uint64_t full[MAX_STAGES];
+    uint64_t empty[MAX_STAGES];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
@@ -50,12 +49,17 @@ struct __align__(16) SmemCtl {
     __align__(16) float colf[2][MAX_BLOCK_N];
 };
 
-constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * (SMEM_A_STAGE + SMEM_B_STAGE) +
-    sizeof(SmemCtl);
+// 227 KiB per CTA: alignment slack + control block + as many (A tile, B tile) stages as fit
+constexpr size_t SMEM_BYTES = 232448;
+// u8 tiles leave through TMA stores: each epilogue warp stages 32 rows x 64 bytes (64-byte swizzle)
+constexpr int STAGING_PER_WARP = 32 * 64;
+constexpr size_t SMEM_STAGING_BYTES = (size_t)EPI_WARPS * STAGING_PER_WARP;  // 16 KiB
+constexpr size_t SMEM_RING_BYTES = (SMEM_BYTES - 1024 - sizeof(SmemCtl) - SMEM_STAGING_BYTES) & ~(size_t)1023;
 
 struct Params {
     uint32_t M, N, K;
     uint32_t block_n;       // multiple of 32, <= 256
+    uint32_t stages;        // pipeline depth, <= MAX_STAGES
     uint32_t tiles_m, tiles_n, num_kb;
     void *C;
     GemmEpilogue ep;
@@ -68,6 +72,31 @@ struct Params {
 // branches and small, because each epilogue warp runs it 4 to 8 times per tile back to back and
 // the instruction stream has to stay resident.  Per element: add offsetC, s32 -> f32 (vcvtdq2ps),
 // multiply (vmulps), then for u8 the bias-add rounding of f32_to_u8_zp128.
+// 32 accumulators of one row -> 32 bytes (8 words): +offsetC, s32 -> f32, * factor, round, +128, clamp
+__device__ __forceinline__ void chunk_to_u8(const int32_t *offs, const float *colf, uint32_t cl, const uint32_t (&r)[32],
+    uint32_t (&w)[8])
+{
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+        const int4 o = *reinterpret_cast<const int4 *>(offs + cl + j);
+        const float4 c4 = *reinterpret_cast<const float4 *>(colf + cl + j);
+        const uint32_t b0 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j] + o.x), c4.x));
+        const uint32_t b1 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j + 1] + o.y), c4.y));
+        const uint32_t b2 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j + 2] + o.z), c4.z));
+        const uint32_t b3 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j + 3] + o.w), c4.w));
+        w[j >> 2] = b0 + (b1 << 8) + (b2 << 16) + (b3 << 24);
+    }
+}
+// 32 bytes of row `lane` into the warp's staging box [32 rows][64 B], 64-byte swizzle: the 16-byte
+// chunk index is XORed with bits 1..2 of the row, the pattern the TMA store undoes
+__device__ __forceinline__ void stage_u8(uint8_t *stg, uint32_t lane, uint32_t which, const uint32_t (&w)[8])
+{
+    const uint32_t sw = (lane >> 1) & 3;
+    uint8_t *row = stg + lane * 64;
+    *reinterpret_cast<uint4 *>(row + (((which * 2) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<uint4 *>(row + (((which * 2 + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+}
+
 template <int KIND>
 __device__ __forceinline__ void store_chunk_fast(void *C, uint32_t N, const int32_t *offs, const float *colf,
     uint32_t m, uint32_t n0, uint32_t cl, const uint32_t (&r)[32])
@@ -75,16 +104,7 @@ __device__ __forceinline__ void store_chunk_fast(void *C, uint32_t N, const int3
     const size_t row_off = (size_t)m * N + n0;
     if (KIND == 2) {
         uint32_t w[8];
-#pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-            const int4 o = *reinterpret_cast<const int4 *>(offs + cl + j);
-            const float4 c4 = *reinterpret_cast<const float4 *>(colf + cl + j);
-            const uint32_t b0 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j] + o.x), c4.x));
-            const uint32_t b1 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j + 1] + o.y), c4.y));
-            const uint32_t b2 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j + 2] + o.z), c4.z));
-            const uint32_t b3 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j + 3] + o.w), c4.w));
-            w[j >> 2] = b0 + (b1 << 8) + (b2 << 16) + (b3 << 24);
-        }
+        chunk_to_u8(offs, colf, cl, r, w);
         uint8_t *out = reinterpret_cast<uint8_t *>(C) + row_off;
         *reinterpret_cast<uint4 *>(out) = make_uint4(w[0], w[1], w[2], w[3]);
         *reinterpret_cast<uint4 *>(out + 16) = make_uint4(w[4], w[5], w[6], w[7]);
@@ -230,18 +250,21 @@ __device__ __forceinline__ void store_chunk(const Params &p, const int32_t *offs
     }
 }
 
-// KIND >= 0: the fast epilogue for that output kind (0 s32, 1 f32, 2 u8); KIND < 0: the general one.
+// KIND >= 0: the fast epilogue for that output kind (0 s32, 1 f32, 2 u8 with direct stores, 3 u8 through
+// swizzled staging + TMA stores described by map_c); KIND < 0: the general one.
 template <int KIND>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-    const Params p)
+    const __grid_constant__ CUtensorMap map_c, const Params p)
 {
     extern __shared__ uint8_t smem_raw[];
     // 128-byte swizzled tiles need 1024-byte aligned bases
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *smem_a = smem;
-    uint8_t *smem_b = smem + STAGES * SMEM_A_STAGE;
-    SmemCtl *ctl = reinterpret_cast<SmemCtl *>(smem + STAGES * (SMEM_A_STAGE + SMEM_B_STAGE));
+    const uint32_t b_stage = p.block_n * BLOCK_K;  // multiple of 4 KiB: every stage stays 1024-byte aligned
+    uint8_t *smem_b = smem + p.stages * SMEM_A_STAGE;
+    uint8_t *smem_staging = smem + SMEM_RING_BYTES;  // 1024-byte aligned
+    SmemCtl *ctl = reinterpret_cast<SmemCtl *>(smem + SMEM_RING_BYTES + SMEM_STAGING_BYTES);
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
@@ -249,7 +272,7 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const uint32_t stage_bytes = (uint32_t)(BLOCK_M + p.block_n) * BLOCK_K;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < MAX_STAGES; ++s) {
             mbar_init(&ctl->full[s], 1);
             mbar_init(&ctl->empty[s], 1);
         }
@@ -287,8 +310,8 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     }
                     mbar_expect_tx(&ctl->full[stage], stage_bytes);
                     tma_load_2d(&map_a, &ctl->full[stage], smem_a + stage * SMEM_A_STAGE, (int)(kb * BLOCK_K), m0);
-                    tma_load_2d(&map_b, &ctl->full[stage], smem_b + stage * SMEM_B_STAGE, (int)(kb * BLOCK_K), n0);
-                    if (++stage == STAGES) {
+                    tma_load_2d(&map_b, &ctl->full[stage], smem_b + stage * b_stage, (int)(kb * BLOCK_K), n0);
+                    if (++stage == p.stages) {
                         stage = 0;
                         phase ^= 1;
                     }
@@ -323,7 +346,7 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     }
                     tcgen05_fence_after();
                     const uint64_t da = make_desc_sw128(smem_u32(smem_a + stage * SMEM_A_STAGE));
-                    const uint64_t db = make_desc_sw128(smem_u32(smem_b + stage * SMEM_B_STAGE));
+                    const uint64_t db = make_desc_sw128(smem_u32(smem_b + stage * b_stage));
 #pragma unroll
                     for (uint32_t k = 0; k < BLOCK_K / UMMA_K; ++k) {
                         // advancing K inside the 128-byte swizzle row: +32 bytes = +2 in the
@@ -331,7 +354,7 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                         umma_i8(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
                     }
                     tcgen05_commit(&ctl->empty[stage]);  // frees the stage once these MMAs retire
-                    if (++stage == STAGES) {
+                    if (++stage == p.stages) {
                         stage = 0;
                         phase ^= 1;
                     }
@@ -352,6 +375,7 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         const uint32_t quad = warp & 3;         // tensor-memory lane quadrant this warp may read
         const uint32_t half = (warp - 2) >> 2;  // which half of the tile's columns
         const uint32_t et = threadIdx.x - 64;   // 0..255
+        uint8_t *stg = smem_staging + (warp - 2) * STAGING_PER_WARP;
         const GemmEpilogue &ep = p.ep;
         const uint32_t nch = p.block_n >> 5;
         const uint32_t c_begin = half ? ((nch + 1) >> 1) : 0u;
@@ -442,7 +466,20 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     mbar_arrive(&ctl->tmem_empty[acc]);  // accumulator fully read: the MMA may reuse it
                     released = true;
                 }
-                if (row_ok && n0 + c * 32 < p.N) {
+                if (KIND == 3) {
+                    if (has1) {
+                        // first half of a 64-column box: the previous box must have left the staging buffer
+                        if (lane == 0) {
+                            tma_store_wait_read();
+                        }
+                        __syncwarp();
+                        uint32_t w[8];
+                        chunk_to_u8(offs, colf, c * 32, ra, w);
+                        stage_u8(stg, lane, 0, w);
+                    } else if (row_ok && n0 + c * 32 < p.N) {
+                        store_chunk_fast<2>(p.C, p.N, offs, colf, m, n0 + c * 32, c * 32, ra);  // odd chunk out
+                    }
+                } else if (row_ok && n0 + c * 32 < p.N) {
                     if (KIND >= 0) {
                         store_chunk_fast<KIND>(p.C, p.N, offs, colf, m, n0 + c * 32, c * 32, ra);
                     } else {
@@ -458,7 +495,17 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                         mbar_arrive(&ctl->tmem_empty[acc]);
                         released = true;
                     }
-                    if (row_ok && n0 + (c + 1) * 32 < p.N) {
+                    if (KIND == 3) {
+                        uint32_t w[8];
+                        chunk_to_u8(offs, colf, (c + 1) * 32, rb, w);
+                        stage_u8(stg, lane, 1, w);
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0 && n0 + c * 32 < p.N) {
+                            // rows beyond M and columns beyond N are clipped by the tensor map
+                            tma_store_2d(&map_c, stg, (int)(n0 + c * 32), (int)(m0 + quad * 32));
+                        }
+                    } else if (row_ok && n0 + (c + 1) * 32 < p.N) {
                         if (KIND >= 0) {
                             store_chunk_fast<KIND>(p.C, p.N, offs, colf, m, n0 + (c + 1) * 32, (c + 1) * 32, rb);
                         } else {
@@ -476,6 +523,10 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 ctl->colf[acc ^ 1][et] = factor_of(sb_next);
             }
         }
+        if (KIND == 3 && lane == 0) {
+            tma_store_wait_all();  // shared memory and the output must be settled before the CTA leaves
+        }
+        __syncwarp();
     }
 
     __syncthreads();
@@ -521,7 +572,7 @@ bool make_map(CUtensorMap *map, const void *base, uint64_t inner, uint64_t rows,
     const uint64_t strides[1] = {pitch};
     const uint32_t box[2] = {(uint32_t)BLOCK_K, box_rows};
     const uint32_t estr[2] = {1, 1};
-    return encode_tiled_u8(map, 2, base, dims, strides, box, estr, true);
+    return encode_tiled_u8(map, 2, base, dims, strides, box, estr, 128);
 }
 
 // Tile width: the widest of 256 / 192 / 128 / 64 / 32 columns that still gives every SM a tile,
@@ -556,7 +607,7 @@ bool tensor_map_encoder_available()
 }
 
 bool encode_tiled_u8(void *map, uint32_t rank, const void *base, const uint64_t *dims, const uint64_t *strides,
-    const uint32_t *box, const uint32_t *elem_strides, bool swizzle128)
+    const uint32_t *box, const uint32_t *elem_strides, int swizzle_bytes)
 {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) {
@@ -573,7 +624,8 @@ bool encode_tiled_u8(void *map, uint32_t rank, const void *base, const uint64_t 
         }
     }
     CUresult r = fn(reinterpret_cast<CUtensorMap *>(map), CU_TENSOR_MAP_DATA_TYPE_UINT8, rank, const_cast<void *>(base), d,
-        st, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+        st, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+            : (swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
@@ -604,8 +656,9 @@ EE launch_gemm_tcgen05(uint32_t M, uint32_t N, uint32_t K, const uint8_t *A, con
     static std::once_flag attr_once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(attr_once, [] {
-        const void *kernels[4] = {(const void *)gemm_u8s8_tcgen05_kernel<-1>, (const void *)gemm_u8s8_tcgen05_kernel<0>,
-            (const void *)gemm_u8s8_tcgen05_kernel<1>, (const void *)gemm_u8s8_tcgen05_kernel<2>};
+        const void *kernels[5] = {(const void *)gemm_u8s8_tcgen05_kernel<-1>, (const void *)gemm_u8s8_tcgen05_kernel<0>,
+            (const void *)gemm_u8s8_tcgen05_kernel<1>, (const void *)gemm_u8s8_tcgen05_kernel<2>,
+            (const void *)gemm_u8s8_tcgen05_kernel<3>};
         for (const void *k : kernels) {
             cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
             if (e != cudaSuccess) {
@@ -620,6 +673,10 @@ EE launch_gemm_tcgen05(uint32_t M, uint32_t N, uint32_t K, const uint8_t *A, con
     p.N = N;
     p.K = K;
     p.block_n = pick_block_n(M, N, c->sm_count);
+    p.stages = (uint32_t)(SMEM_RING_BYTES / (SMEM_A_STAGE + (size_t)p.block_n * BLOCK_K));
+    if (p.stages > (uint32_t)MAX_STAGES) {
+        p.stages = MAX_STAGES;
+    }
     p.tiles_m = (M + BLOCK_M - 1) / BLOCK_M;
     p.tiles_n = (N + p.block_n - 1) / p.block_n;
     p.num_kb = (K + BLOCK_K - 1) / BLOCK_K;
@@ -640,14 +697,26 @@ EE launch_gemm_tcgen05(uint32_t M, uint32_t N, uint32_t K, const uint8_t *A, con
     // conversion factor per column
     const bool fast = p.vec_ok && (N % 32 == 0) && !(ep.out_kind != 2 && ep.accumulate) &&
         !(ep.per_channel && ep.row_scale != nullptr);
+    // u8 output: 32-row x 64-byte boxes, 64-byte swizzle, stored by TMA from the epilogue's staging
+    CUtensorMap map_c = map_a;  // placeholder for the kinds that never touch it
+    bool tma_c = false;
+    if (fast && ep.out_kind == 2) {
+        const uint64_t dims[2] = {N, M};
+        const uint64_t strides[1] = {N};
+        const uint32_t box[2] = {64, 32};
+        const uint32_t estr[2] = {1, 1};
+        tma_c = encode_tiled_u8(&map_c, 2, C, dims, strides, box, estr, 64);
+    }
     if (!fast) {
-        gemm_u8s8_tcgen05_kernel<-1><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
+        gemm_u8s8_tcgen05_kernel<-1><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, map_c, p);
     } else if (ep.out_kind == 0) {
-        gemm_u8s8_tcgen05_kernel<0><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
+        gemm_u8s8_tcgen05_kernel<0><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, map_c, p);
     } else if (ep.out_kind == 1) {
-        gemm_u8s8_tcgen05_kernel<1><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
+        gemm_u8s8_tcgen05_kernel<1><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, map_c, p);
+    } else if (tma_c) {
+        gemm_u8s8_tcgen05_kernel<3><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, map_c, p);
     } else {
-        gemm_u8s8_tcgen05_kernel<2><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
+        gemm_u8s8_tcgen05_kernel<2><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, map_c, p);
     }
     count_launch();
     B200_CUDA(cudaGetLastError());

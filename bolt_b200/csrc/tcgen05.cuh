@@ -161,6 +161,31 @@ __device__ __forceinline__ void tma_load_5d(const CUtensorMap *map, uint64_t *ba
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
         : "memory");
 }
+
+// ---- TMA store (shared -> global) of a 2-D box, bulk-group completion -----------------------
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, const void *src, int x, int y)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// all earlier bulk stores of this thread have finished READING shared memory
+__device__ __forceinline__ void tma_store_wait_read()
+{
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+// all earlier bulk stores of this thread are complete
+__device__ __forceinline__ void tma_store_wait_all()
+{
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+// make generic-proxy writes to shared memory visible to the async proxy (TMA)
+__device__ __forceinline__ void fence_proxy_async_smem()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 // Shared-memory matrix descriptor, K-major operand without swizzle: 8 rows x 16 bytes form one
 // contiguous 128-byte core matrix; `sbo` bytes between 8-row groups, `lbo` bytes between the
 // 16-byte K chunks.
