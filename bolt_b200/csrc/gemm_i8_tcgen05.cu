@@ -44,9 +44,9 @@ struct __align__(16) SmemCtl {
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
-    // column constants of the current tile, double buffered by accumulator
-    __align__(16) int32_t offs[2][MAX_BLOCK_N];
-    __align__(16) float colf[2][MAX_BLOCK_N];
+    // per epilogue warp: offsetC and conversion factor of the (at most 128) columns it owns
+    __align__(16) int32_t offs[EPI_WARPS][128];
+    __align__(16) float colf[EPI_WARPS][128];
 };
 
 // 227 KiB per CTA: alignment slack + control block + as many (A tile, B tile) stages as fit
@@ -84,7 +84,7 @@ __device__ __forceinline__ void chunk_to_u8(const int32_t *offs, const float *co
         const uint32_t b1 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j + 1] + o.y), c4.y));
         const uint32_t b2 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j + 2] + o.z), c4.z));
         const uint32_t b3 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j + 3] + o.w), c4.w));
-        w[j >> 2] = b0 + (b1 << 8) + (b2 << 16) + (b3 << 24);
+        w[j >> 2] = __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
     }
 }
 // 32 bytes of row `lane` into the warp's staging box [32 rows][64 B], 64-byte swizzle: the 16-byte
@@ -374,28 +374,35 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         // ------------------------------- epilogue warps 2..9 ------------------------------------
         const uint32_t quad = warp & 3;         // tensor-memory lane quadrant this warp may read
         const uint32_t half = (warp - 2) >> 2;  // which half of the tile's columns
-        const uint32_t et = threadIdx.x - 64;   // 0..255
         uint8_t *stg = smem_staging + (warp - 2) * STAGING_PER_WARP;
         const GemmEpilogue &ep = p.ep;
         const uint32_t nch = p.block_n >> 5;
         const uint32_t c_begin = half ? ((nch + 1) >> 1) : 0u;
         const uint32_t c_end = half ? nch : ((nch + 1) >> 1);
-        // Column constants (offsetC and the conversion factor) of a tile live in shared memory,
-        // double buffered by accumulator.  Thread `et` owns column `et`: it fetches the next tile's
-        // values into registers before it waits for the current accumulator, and parks them in the
-        // other buffer after the tile, so the global-load latency never sits on the critical path.
+        // Column constants (offsetC and the conversion factor): every warp keeps those of its own
+        // columns in its own slice of shared memory, lane l owning columns l, l+32, l+64, l+96 of the
+        // warp's range.  The next tile's values are fetched into registers before the current
+        // accumulator is awaited and written after the tile's chunks, so neither the global-load
+        // latency nor any CTA-wide barrier sits between two tiles; warps drift freely.
         // The loads are volatile asm so that they stay where they are written (early); everything
         // that depends on them is written after the tile's chunks (late).
-        auto fetch_raw = [&](uint32_t tile_n0, int32_t &o, float &sb) {
-            o = 0;
-            sb = ep.sB;
-            const uint32_t n = tile_n0 + et;
-            if (et < p.block_n && n < p.N) {
-                if (ep.offsetC != nullptr) {
-                    asm volatile("ld.global.nc.b32 %0, [%1];" : "=r"(o) : "l"(ep.offsetC + n));
-                }
-                if (ep.per_channel && ep.col_scale != nullptr) {
-                    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(sb) : "l"(ep.col_scale + n));
+        int32_t *offs = ctl->offs[warp - 2];
+        float *colf = ctl->colf[warp - 2];
+        const uint32_t my_cols = (c_end - c_begin) * 32;
+        auto fetch_raw = [&](uint32_t tile_n0, int32_t (&o)[4], float (&sb)[4]) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                o[q] = 0;
+                sb[q] = ep.sB;
+                const uint32_t j = lane + 32 * q;
+                const uint32_t n = tile_n0 + c_begin * 32 + j;
+                if (j < my_cols && n < p.N) {
+                    if (ep.offsetC != nullptr) {
+                        asm volatile("ld.global.nc.b32 %0, [%1];" : "=r"(o[q]) : "l"(ep.offsetC + n));
+                    }
+                    if (ep.per_channel && ep.col_scale != nullptr) {
+                        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(sb[q]) : "l"(ep.col_scale + n));
+                    }
                 }
             }
         };
@@ -410,12 +417,19 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             // with per-row scales the division is done per element; keep sB here
             return ep.row_scale ? sb : __fdiv_rn(ep.num, __fmul_rn(sa_dev, sb));
         };
+        auto park = [&](const int32_t (&o)[4], const float (&sb)[4]) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                offs[lane + 32 * q] = o[q];
+                colf[lane + 32 * q] = factor_of(sb[q]);
+            }
+            __syncwarp();
+        };
         if (blockIdx.x < num_tiles) {
-            int32_t o;
-            float sb;
+            int32_t o[4];
+            float sb[4];
             fetch_raw((blockIdx.x / p.tiles_m) * p.block_n, o, sb);
-            ctl->offs[0][et] = o;
-            ctl->colf[0][et] = factor_of(sb);
+            park(o, sb);
         }
         uint32_t it = 0;
         for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
@@ -423,18 +437,12 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             const uint32_t acc_phase = (it >> 1) & 1;
             const uint32_t m0 = (tile % p.tiles_m) * BLOCK_M;
             const uint32_t n0 = (tile / p.tiles_m) * p.block_n;
-            const int32_t *offs = ctl->offs[acc];
-            const float *colf = ctl->colf[acc];
-            // Once per tile, all epilogue threads: makes this tile's constants visible and proves that
-            // everyone is done with the other buffer.  A warp whose wait ran out keeps arriving here,
-            // and all of them leave together once the flag is visible.
-            asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
             if (*reinterpret_cast<volatile uint32_t *>(&ctl->abort_flag) != 0) {
-                break;
+                break;  // some role's bounded wait ran out
             }
             const uint32_t next_tile = tile + gridDim.x;
-            int32_t o_next = 0;
-            float sb_next = 0.f;
+            int32_t o_next[4];
+            float sb_next[4];
             if (next_tile < num_tiles) {
                 fetch_raw((next_tile / p.tiles_m) * p.block_n, o_next, sb_next);
             }
@@ -445,7 +453,7 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     atomicExch(p.status, 3);
                     atomicExch(&ctl->abort_flag, 1u);
                 }
-                continue;
+                break;
             }
             tcgen05_fence_after();
             const uint32_t m = m0 + quad * 32 + lane;
@@ -474,16 +482,16 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                         }
                         __syncwarp();
                         uint32_t w[8];
-                        chunk_to_u8(offs, colf, c * 32, ra, w);
+                        chunk_to_u8(offs, colf, (c - c_begin) * 32, ra, w);
                         stage_u8(stg, lane, 0, w);
                     } else if (row_ok && n0 + c * 32 < p.N) {
-                        store_chunk_fast<2>(p.C, p.N, offs, colf, m, n0 + c * 32, c * 32, ra);  // odd chunk out
+                        store_chunk_fast<2>(p.C, p.N, offs, colf, m, n0 + c * 32, (c - c_begin) * 32, ra);  // odd chunk out
                     }
                 } else if (row_ok && n0 + c * 32 < p.N) {
                     if (KIND >= 0) {
-                        store_chunk_fast<KIND>(p.C, p.N, offs, colf, m, n0 + c * 32, c * 32, ra);
+                        store_chunk_fast<KIND>(p.C, p.N, offs, colf, m, n0 + c * 32, (c - c_begin) * 32, ra);
                     } else {
-                        store_chunk(p, offs, colf, m, n0 + c * 32, c * 32, ra);
+                        store_chunk(p, offs, colf, m, n0 + c * 32, (c - c_begin) * 32, ra);
                     }
                 }
                 if (has1) {
@@ -497,7 +505,7 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     }
                     if (KIND == 3) {
                         uint32_t w[8];
-                        chunk_to_u8(offs, colf, (c + 1) * 32, rb, w);
+                        chunk_to_u8(offs, colf, (c + 1 - c_begin) * 32, rb, w);
                         stage_u8(stg, lane, 1, w);
                         fence_proxy_async_smem();
                         __syncwarp();
@@ -507,9 +515,9 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                         }
                     } else if (row_ok && n0 + (c + 1) * 32 < p.N) {
                         if (KIND >= 0) {
-                            store_chunk_fast<KIND>(p.C, p.N, offs, colf, m, n0 + (c + 1) * 32, (c + 1) * 32, rb);
+                            store_chunk_fast<KIND>(p.C, p.N, offs, colf, m, n0 + (c + 1) * 32, (c + 1 - c_begin) * 32, rb);
                         } else {
-                            store_chunk(p, offs, colf, m, n0 + (c + 1) * 32, (c + 1) * 32, rb);
+                            store_chunk(p, offs, colf, m, n0 + (c + 1) * 32, (c + 1 - c_begin) * 32, rb);
                         }
                     }
                 }
@@ -519,8 +527,8 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 mbar_arrive(&ctl->tmem_empty[acc]);
             }
             if (next_tile < num_tiles) {
-                ctl->offs[acc ^ 1][et] = o_next;
-                ctl->colf[acc ^ 1][et] = factor_of(sb_next);
+                __syncwarp();  // every lane is done reading this tile's constants
+                park(o_next, sb_next);
             }
         }
         if (KIND == 3 && lane == 0) {
