@@ -44,7 +44,7 @@ struct __align__(16) SmemCtl {
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
-    __align__(16) int32_t offs[2][MAX_BLOCK_N];
+    __align__(16) int32_t offs[2048];  // offsetC + bias of every output channel (layers with OC <= 2048)
 };
 
 constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * (SMEM_A_STAGE + SMEM_B_STAGE) + sizeof(SmemCtl);
@@ -55,24 +55,49 @@ struct ConvParams {
     uint32_t ICb, FW;
     uint32_t sH, sW, dH, dW;
     uint32_t G;             // K chunks per TMA load: divides both ICb and 8
+    uint32_t merged_w;      // 1: stride-1 rows, map_x is 4-D with (c16, w) merged into one byte dimension
     uint32_t total_chunks;  // taps * ICb
     uint32_t num_kb;        // ceil(total_chunks / 8)
     uint32_t block_n, tiles_n, tiles_m;
     void *out;
     const float *eltwise;
     const int32_t *offs;    // [OC]: offsetC + round(bias * scaleO)
-    float factor;           // 1 / scaleO
+    float factor;           // 1 / scaleO (fp32 output) or outScale / scaleO (fused u8 output)
     int relu;
     int *status;
 };
 
 // KIND 1: fp32 output (dequantize, + eltwise, ReLU).  KIND 0: int32 output after ReLU, the staging
-// buffer of the u8 path (convolution_direct.cpp:2689-2693).
+// buffer of the dynamic u8 path (convolution_direct.cpp:2689-2693).  KIND 2: u8 output with a known
+// output scale, the arithmetic of quantizeI32ToU8 with both scales given (avx512/quantize.cpp:372-414:
+// vcvtdq2ps, vmulps, vaddps 128, vcvtps2dq, vpmovusdb) fused behind the ReLU.
 template <int KIND>
 __device__ __forceinline__ void store_block16(const ConvParams &p, const int32_t *offs, size_t base, uint32_t width,
     const uint32_t *r /*16 accumulators*/)
 {
-    if (KIND == 1) {
+    if (KIND == 2) {
+        uint8_t *out = reinterpret_cast<uint8_t *>(p.out) + base;
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 16; j += 4) {
+            const int4 o = *reinterpret_cast<const int4 *>(offs + j);
+            int v[4] = {(int)r[j] + o.x, (int)r[j + 1] + o.y, (int)r[j + 2] + o.z, (int)r[j + 3] + o.w};
+            uint32_t b[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const int a = p.relu ? max(v[t], 0) : v[t];
+                const float f = __fadd_rn(__fmul_rn(__int2float_rn(a), p.factor), 128.0f);
+                // rne(f) as unsigned, clamped at 255: negatives wrap above 255 like vpmovusdb reads them
+                b[t] = min(__float_as_uint(__fadd_rn(f, 12582912.0f)) - 0x4B400000u, 255u);
+            }
+            w[j >> 2] = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+        }
+        if (width == 16) {
+            *reinterpret_cast<uint4 *>(out) = make_uint4(w[0], w[1], w[2], w[3]);
+        } else {
+            *reinterpret_cast<uint2 *>(out) = make_uint2(w[0], w[1]);
+        }
+    } else if (KIND == 1) {
         float *out = reinterpret_cast<float *>(p.out) + base;
 #pragma unroll
         for (int j = 0; j < 16; j += 4) {
@@ -186,8 +211,15 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                         const uint32_t tap = q / p.ICb;
                         const uint32_t cb = q - tap * p.ICb;
                         const uint32_t kh = tap / p.FW, kw = tap - kh * p.FW;
-                        tma_load_5d(&map_x, &ctl->full[stage], smem_a + stage * SMEM_A_STAGE + j * CHUNK_BYTES, 0,
-                            (int)(ow0 * p.sW + kw * p.dW), (int)(oh0 * p.sH + kh * p.dH), (int)cb, (int)n);
+                        uint8_t *dst = smem_a + stage * SMEM_A_STAGE + j * CHUNK_BYTES;
+                        if (p.merged_w) {
+                            // a row of TW pixels is TW * 16 contiguous bytes: one wide request per row
+                            tma_load_4d(&map_x, &ctl->full[stage], dst, (int)((ow0 + kw * p.dW) * 16),
+                                (int)(oh0 * p.sH + kh * p.dH), (int)cb, (int)n);
+                        } else {
+                            tma_load_5d(&map_x, &ctl->full[stage], dst, 0, (int)(ow0 * p.sW + kw * p.dW),
+                                (int)(oh0 * p.sH + kh * p.dH), (int)cb, (int)n);
+                        }
                     }
                     tma_load_2d(&map_w, &ctl->full[stage], smem_b + stage * SMEM_B_STAGE, (int)(kb * BLOCK_K), (int)n0);
                     if (++stage == STAGES) {
@@ -256,6 +288,16 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         const uint32_t half = (warp - 2) >> 2;
         const uint32_t et = threadIdx.x - 64;
         const uint32_t nch = p.block_n >> 5;
+        // Per-channel offsets: staged once per CTA when they fit, so that no tile waits on a global
+        // load or a CTA-wide barrier; wider layers read them through L1.
+        const int32_t *offs_all = p.offs;
+        if (p.OC <= 2048) {
+            for (uint32_t i = et; i < 2048; i += EPI_THREADS) {
+                ctl->offs[i] = (i < p.OC) ? p.offs[i] : 0;
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+            offs_all = ctl->offs;
+        }
         const uint32_t c_begin = half ? ((nch + 1) >> 1) : 0u;
         const uint32_t c_end = half ? nch : ((nch + 1) >> 1);
         uint32_t it = 0;
@@ -264,14 +306,8 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             const uint32_t acc_phase = (it >> 1) & 1;
             uint32_t n, oh0, ow0, n0;
             decode(tile, n, oh0, ow0, n0);
-            int32_t *offs = ctl->offs[acc];
-            if (et < p.block_n) {
-                const uint32_t oc = n0 + et;
-                offs[et] = (oc < p.OC) ? p.offs[oc] : 0;
-            }
-            asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
             if (*reinterpret_cast<volatile uint32_t *>(&ctl->abort_flag) != 0) {
-                break;
+                break;  // some role's bounded wait ran out
             }
             bool ok = mbar_wait(&ctl->tmem_full[acc], acc_phase);
             ok = __all_sync(0xffffffffu, ok);
@@ -280,7 +316,7 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                     atomicExch(p.status, 13);
                     atomicExch(&ctl->abort_flag, 1u);
                 }
-                continue;
+                break;
             }
             tcgen05_fence_after();
             const uint32_t r = quad * 32 + lane;
@@ -290,14 +326,7 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             const size_t pix = (size_t)oh * p.OW + ow;
             const size_t plane = (size_t)p.OH * p.OW;
             const uint32_t tbase = tmem_base + ((quad * 32u) << 16) + acc * MAX_BLOCK_N;
-            for (uint32_t c = c_begin; c < c_end; ++c) {
-                uint32_t rr[32];
-                tmem_ld32(tbase + c * 32, rr);
-                tmem_ld_wait(rr);
-                if (c + 1 == c_end) {
-                    tcgen05_fence_before();
-                    mbar_arrive(&ctl->tmem_empty[acc]);
-                }
+            auto emit = [&](uint32_t c, const uint32_t *rr) {
                 if (row_ok) {
 #pragma unroll
                     for (int hb = 0; hb < 2; ++hb) {
@@ -305,9 +334,36 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                         if (ocb < p.OC) {
                             const uint32_t width = min(16u, p.OC - ocb);
                             const size_t base = ((size_t)n * p.OC + ocb) * plane + pix * width;
-                            store_block16<KIND>(p, offs + c * 32 + hb * 16, base, width, rr + hb * 16);
+                            store_block16<KIND>(p, offs_all + ocb, base, width, rr + hb * 16);
                         }
                     }
+                }
+            };
+            // two register buffers: the next chunk is on its way from tensor memory while this one is
+            // converted and stored; the accumulator is released as soon as its last chunk has arrived
+            uint32_t ra[32], rb[32];
+            if (c_begin < c_end) {
+                tmem_ld32(tbase + c_begin * 32, ra);
+            }
+            for (uint32_t c = c_begin; c < c_end; c += 2) {
+                tmem_ld_wait(ra);
+                const bool has1 = c + 1 < c_end;
+                if (has1) {
+                    tmem_ld32(tbase + (c + 1) * 32, rb);
+                } else {
+                    tcgen05_fence_before();
+                    mbar_arrive(&ctl->tmem_empty[acc]);
+                }
+                emit(c, ra);
+                if (has1) {
+                    tmem_ld_wait(rb);
+                    if (c + 2 < c_end) {
+                        tmem_ld32(tbase + (c + 2) * 32, ra);
+                    } else {
+                        tcgen05_fence_before();
+                        mbar_arrive(&ctl->tmem_empty[acc]);
+                    }
+                    emit(c + 1, rb);
                 }
             }
             if (c_begin >= c_end) {
@@ -505,7 +561,7 @@ EE conv_geometry(const TensorDesc *inputDesc, const TensorDesc *filterDesc, cons
 }  // namespace
 
 // run the implicit-GEMM kernel; xp: [N][ICb][Hp][Wp][16] u8, w: [OCr][K] s8, offs: [OC] int32 (all device)
-EE launch_conv_tcgen05(const uint8_t *xp, const int8_t *w, const int32_t *offs, void *out, int out_f32,
+EE launch_conv_tcgen05(const uint8_t *xp, const int8_t *w, const int32_t *offs, void *out, int out_kind,
     const float *eltwise, float factor, int relu, uint32_t N, uint32_t ICb, uint32_t Hp, uint32_t Wp, uint32_t OC,
     uint32_t OCr, uint32_t OH, uint32_t OW, uint32_t FH, uint32_t FW, uint32_t sH, uint32_t sW, uint32_t dH,
     uint32_t dW, cudaStream_t st)
@@ -517,7 +573,8 @@ EE launch_conv_tcgen05(const uint8_t *xp, const int8_t *w, const int32_t *offs, 
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
-        const void *ks[2] = {(const void *)conv_u8s8_tcgen05_kernel<0>, (const void *)conv_u8s8_tcgen05_kernel<1>};
+        const void *ks[3] = {(const void *)conv_u8s8_tcgen05_kernel<0>, (const void *)conv_u8s8_tcgen05_kernel<1>,
+            (const void *)conv_u8s8_tcgen05_kernel<2>};
         for (const void *k : ks) {
             cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
             if (e != cudaSuccess) {
@@ -536,14 +593,18 @@ EE launch_conv_tcgen05(const uint8_t *xp, const int8_t *w, const int32_t *offs, 
     p.OW = OW;
     p.OC = OC;
     // output patch of 128 pixels: the shape that wastes the fewest rows
+    // With stride 1 along W a row of TW pixels is TW*16 contiguous bytes; the (c16, w) dimensions are
+    // then merged so that TMA moves one 16*TW-byte run per row instead of TW 16-byte ones (a TMA box
+    // is at most 256 elements wide, hence TW <= 16 on that path).
+    const bool merged_w = (sW == 1);
     uint32_t best_tw = 128, best_tiles = 0xFFFFFFFFu;
-    for (uint32_t tw = 128; tw >= 1; tw >>= 1) {
+    for (uint32_t tw = merged_w ? 16 : 128; tw >= 1; tw >>= 1) {
         const uint32_t th = 128 / tw;
         if (tw * sW > 256 || th * sH > 256) {
             continue;
         }
         const uint32_t tiles = ((OW + tw - 1) / tw) * ((OH + th - 1) / th);
-        if (tiles < best_tiles || (tiles == best_tiles && tw > best_tw && tw <= 32)) {
+        if (tiles < best_tiles) {
             best_tiles = tiles;
             best_tw = tw;
         }
@@ -565,6 +626,7 @@ EE launch_conv_tcgen05(const uint8_t *xp, const int8_t *w, const int32_t *offs, 
     p.sW = sW;
     p.dH = dH;
     p.dW = dW;
+    p.merged_w = merged_w ? 1 : 0;
     p.G = 8;
     while (ICb % p.G != 0) {
         p.G >>= 1;
@@ -582,7 +644,15 @@ EE launch_conv_tcgen05(const uint8_t *xp, const int8_t *w, const int32_t *offs, 
     p.status = c->d_status;
 
     CUtensorMap map_x, map_w;
-    {
+    if (merged_w) {
+        const uint64_t dims[4] = {(uint64_t)Wp * 16, Hp, ICb, N};
+        const uint64_t strides[3] = {(uint64_t)Wp * 16, (uint64_t)Hp * Wp * 16, (uint64_t)ICb * Hp * Wp * 16};
+        const uint32_t box[4] = {p.TW * 16, p.TH * sH, p.G, 1};
+        const uint32_t es[4] = {1, sH, 1, 1};
+        if (!encode_tiled_u8(&map_x, 4, xp, dims, strides, box, es, 0)) {
+            return NOT_SUPPORTED;
+        }
+    } else {
         const uint64_t dims[5] = {16, Wp, Hp, ICb, N};
         const uint64_t strides[4] = {16, (uint64_t)Wp * 16, (uint64_t)Hp * Wp * 16, (uint64_t)ICb * Hp * Wp * 16};
         const uint32_t box[5] = {16, p.TW * sW, p.TH * sH, p.G, 1};
@@ -603,7 +673,9 @@ EE launch_conv_tcgen05(const uint8_t *xp, const int8_t *w, const int32_t *offs, 
     }
     const uint64_t tiles = (uint64_t)p.tiles_m * p.tiles_n;
     const uint32_t grid = (uint32_t)(tiles < (uint64_t)c->sm_count ? tiles : (uint64_t)c->sm_count);
-    if (out_f32) {
+    if (out_kind == 2) {
+        conv_u8s8_tcgen05_kernel<2><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_x, map_w, p);
+    } else if (out_kind == 1) {
         conv_u8s8_tcgen05_kernel<1><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_x, map_w, p);
     } else {
         conv_u8s8_tcgen05_kernel<0><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_x, map_w, p);
@@ -817,11 +889,18 @@ EE conv_i8_run(const TensorDesc *inputDesc, void *input, void *eltwiseInput, con
     conv_bias_offset_kernel<<<(g.out.c + 255) / 256, 256, 0, st>>>(d_bias, reinterpret_cast<const int32_t *>(d_w), g.out.c,
         scaleO, d_offs);
     count_launch();
-    void *kernel_out = out_u8 ? reinterpret_cast<void *>(d_tmp) : d_out;
+    // Extension without a counterpart in the reference's convolution (it always requantizes
+    // dynamically): a positive output scale on entry fuses the requantization into the epilogue,
+    // with the arithmetic Bolt uses when an output scale is known (fully_connected.cpp:479-487 ->
+    // quantizeI32ToU8 with scales {out, scaleO}).
+    const bool fused_u8 = out_u8 && sc[1] > 0;
+    void *kernel_out = (out_u8 && !fused_u8) ? reinterpret_cast<void *>(d_tmp) : d_out;
     B200_EE(launch_conv_tcgen05(xp, reinterpret_cast<const int8_t *>(d_w + 4 * (size_t)g.f.n), d_offs, kernel_out,
-        out_u8 ? 0 : 1, d_elt, factor, relu ? 1 : 0, g.in.n, g.ICb, g.Hp, g.Wp, g.out.c, g.OCr, g.out.h, g.out.w, g.f.h,
+        fused_u8 ? 2 : (out_u8 ? 0 : 1), d_elt, fused_u8 ? sc[1] / scaleO : factor, relu ? 1 : 0, g.in.n, g.ICb, g.Hp, g.Wp, g.out.c, g.OCr, g.out.h, g.out.w, g.f.h,
         g.f.w, g.sH, g.sW, g.dH, g.dW, st));
-    if (out_u8) {
+    if (fused_u8) {
+        // sc[1] stays the caller's output scale
+    } else if (out_u8) {
         // convolution_direct.cpp:2798-2806: dynamic scale over the whole output, scale[1] = scaleO * 127/max
         F32 scales[2] = {-1, scaleO};
         B200_EE(quantize_i32_u8_device(reinterpret_cast<const int32_t *>(kernel_out), out_elems,

@@ -11,7 +11,7 @@ namespace tc {
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 128;         // bytes of K per stage
 constexpr int UMMA_K = 32;           // K per tcgen05.mma.kind::i8
-constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // per wait; far above any legitimate wait
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // per wait, about 2 s; far above any legitimate wait
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
 {
@@ -42,26 +42,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
-// Bounded wait: false when the limit ran out (the caller then aborts the CTA's work).
-__device__ __forceinline__ uint64_t global_ns()
-{
-    uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
+// Bounded wait: false when the limit ran out (the caller then aborts the CTA's work).  The bound is
+// counted in SM clock cycles (clock64 is a plain register read; the global nanosecond timer costs
+// about a microsecond per read and must stay off this path, every role waits several times per tile).
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
 {
     if (mbar_try_wait(bar, parity)) {
         return true;
     }
-    const uint64_t t0 = global_ns();
+    const long long t0 = clock64();
     for (;;) {
-        for (int i = 0; i < 64; ++i) {
+#pragma unroll 1
+        for (int i = 0; i < 256; ++i) {
             if (mbar_try_wait(bar, parity)) {
                 return true;
             }
         }
-        if (global_ns() - t0 > WAIT_LIMIT_NS) {
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
             return false;
         }
     }
@@ -159,6 +156,14 @@ __device__ __forceinline__ void tma_load_5d(const CUtensorMap *map, uint64_t *ba
     asm volatile(
         "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_4d(const CUtensorMap *map, uint64_t *bar, void *dst, int c0, int c1, int c2, int c3)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
 

@@ -136,3 +136,27 @@ def test_conv_batch_independence():
     for i in range(4):
         one, _, _ = conv_gpu((1,) + shape[1:], cases.to_blocked(x[i:i + 1], 16), w, bias, 16, 0, True, cases.CONV_SCALES)
         assert one.tobytes() == full[i * per:(i + 1) * per].tobytes()
+
+
+def test_conv_fused_u8_with_given_output_scale():
+    """Extension: a positive output scale on entry fuses ReLU + requantization into the epilogue.  Checked
+    against the oracle's int32 accumulators pushed through the reference's I32 -> U8_Q arithmetic with
+    both scales given (avx512/quantize.cpp:372-414), the path Bolt's fully-connected layer takes when
+    the output scale is known (fully_connected.cpp:479-487)."""
+    for shape in [(2, 64, 14, 14, 64, 3, 3, 1, 1), (1, 128, 28, 28, 72, 1, 1, 1, 0), (2, 32, 9, 9, 48, 3, 3, 2, 1)]:
+        n, ic, ih, iw, oc, fh, fw, st, pad = shape
+        x = synth.relu_u8(ic + oc, (n, ic, ih, iw))
+        w = (synth.normal(ic * 5 + oc, (oc, ic, fh, fw), 0.05) * 127 / 0.2).clip(-127, 127).round().astype(np.int8)
+        bias = synth.normal(19, (oc,), 0.1)
+        xin = cases.to_blocked(x, 16)
+        s_in, s_out, s_f = 31.75, 9.5, 635.0
+        got, sc, _ = conv_gpu(shape, xin, w, bias, 16, 1, True, [s_in, s_out, s_f])
+        assert sc[1] == s_out
+        s = O.ConvShape(n, ic, ih, iw, oc, fh, fw, st, st, pad, pad, pad, pad, 1, 1, 16, 16, 1, 1)
+        acc = np.zeros(got.size, np.int32)
+        scr = np.array([s_in, -1.0, s_f], np.float32)
+        O.port.oracle_conv_int8(C.byref(s), O.ptr(xin), O.ptr(w), O.ptr(bias), None, O.ptr(np.zeros(got.size, np.uint8)), O.ptr(scr), O.ptr(acc))
+        ref = np.zeros(got.size, np.uint8)
+        sq = np.array([s_out, np.float32(s_in) * np.float32(s_f)], np.float32)
+        O.port.oracle_quantize_i32_u8(O.ptr(acc), acc.size, O.ptr(ref), O.ptr(sq))
+        assert got.tobytes() == ref.tobytes(), shape
