@@ -32,8 +32,8 @@ M_TOKENS, LAYERS, HIDDEN, INTER = 4096, 12, 768, 3072
 OPS_PER_STEP = 2 * M_TOKENS * HIDDEN * INTER * 2 * LAYERS  # 463.86 GOP
 WORKLOAD = "bert_base_int8_linear_stack: 12 x (768->3072->768), M=4096 tokens, s8 per-channel weights, u8 per-tensor activations, fused requant, fp32 out"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of gemm_u8s8_tcgen05_kernel, averaged over
-# the 24 launches of one pass (profiles/gemm_u8s8_tcgen05_bert_stack.md); None until captured.
-GEMM_DRAM_TRAFFIC_PER_LAUNCH = None
+# the 24 launches of one pass (profiles/gemm_u8s8_tcgen05_bert_stack.md).
+GEMM_DRAM_TRAFFIC_PER_LAUNCH = 10274848
 
 
 def measured_peaks():
@@ -189,7 +189,7 @@ def run_b200_arm(args, rank, world, local_rank):
     stack.x_dev.copy_(x_host)
     stack.calibrate()
     B.CHECK_STATUS(lib.bolt_b200_set_pointer_mode(1))
-    flush = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")  # 2 x L2
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device="cuda")  # 256 MiB = 2 x L2; fp32 so that sum() only reads
     sink = []
 
     def evict():

@@ -29,7 +29,20 @@ __global__ void absmax_f32_kernel(const float *__restrict__ x, uint64_t n, unsig
     const bool aligned = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
     uint64_t n4 = aligned ? n / 4 : 0;
     const float4 *x4 = reinterpret_cast<const float4 *>(x);
-    for (uint64_t i = tid; i < n4; i += stride) {
+    uint64_t i = tid;
+    for (; i + 3 * stride < n4; i += 4 * stride) {  // four independent 128-bit loads in flight per thread
+        const float4 a = x4[i], b = x4[i + stride], c = x4[i + 2 * stride], d = x4[i + 3 * stride];
+        const unsigned ma = max(max(__float_as_uint(a.x) & 0x7FFFFFFFu, __float_as_uint(a.y) & 0x7FFFFFFFu),
+            max(__float_as_uint(a.z) & 0x7FFFFFFFu, __float_as_uint(a.w) & 0x7FFFFFFFu));
+        const unsigned mb = max(max(__float_as_uint(b.x) & 0x7FFFFFFFu, __float_as_uint(b.y) & 0x7FFFFFFFu),
+            max(__float_as_uint(b.z) & 0x7FFFFFFFu, __float_as_uint(b.w) & 0x7FFFFFFFu));
+        const unsigned mc = max(max(__float_as_uint(c.x) & 0x7FFFFFFFu, __float_as_uint(c.y) & 0x7FFFFFFFu),
+            max(__float_as_uint(c.z) & 0x7FFFFFFFu, __float_as_uint(c.w) & 0x7FFFFFFFu));
+        const unsigned md = max(max(__float_as_uint(d.x) & 0x7FFFFFFFu, __float_as_uint(d.y) & 0x7FFFFFFFu),
+            max(__float_as_uint(d.z) & 0x7FFFFFFFu, __float_as_uint(d.w) & 0x7FFFFFFFu));
+        m = max(m, max(max(ma, mb), max(mc, md)));
+    }
+    for (; i < n4; i += stride) {
         const float4 v = x4[i];
         m = max(m, __float_as_uint(v.x) & 0x7FFFFFFFu);
         m = max(m, __float_as_uint(v.y) & 0x7FFFFFFFu);

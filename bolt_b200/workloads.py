@@ -32,7 +32,7 @@ class Timer:
     def __init__(self):
         torch = _torch()
         self.torch = torch
-        self.flush = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")
+        self.flush = torch.zeros(64 << 20, dtype=torch.float32, device="cuda")  # 256 MiB; fp32 so that sum() only reads
 
     def evict(self):
         self.sink = self.flush.sum()
