@@ -8,7 +8,9 @@ dynamic per-tensor u8 quantization of the fp32 input, 24 u8 x s8 GEMMs with per-
 weight scales and fused requantization to u8 between layers, fp32 output.  Synthetic seeded data.
 
 `value`  : int8 GEMM TOP/s (2*M*N*K ops of the 24 GEMMs) with the input resident in HBM,
-           the whole step replayed as one CUDA graph, L2 flushed between timed steps.
+           the whole step replayed as one CUDA graph, L2 flushed between timed steps.  One GEMM launch
+           per layer by default; --fused runs the 24 GEMMs inside one persistent cooperative kernel
+           (bolt_b200_linear_stack_run), which measures the same on B200.
 `e2e`    : the same metric through LinearStack.run_host: pinned host input -> H2D -> step -> D2H.
 `roofline`: the tcgen05 GEMM kernel alone (24 launches per pass) against 2 x the measured bf16 peak.
 `cpu_baseline` / --impl reference: the reference's own x86 AVX512-VNNI code (or the scalar oracle
@@ -34,6 +36,9 @@ WORKLOAD = "bert_base_int8_linear_stack: 12 x (768->3072->768), M=4096 tokens, s
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of gemm_u8s8_tcgen05_kernel, averaged over
 # the 24 launches of one pass (profiles/gemm_u8s8_tcgen05_bert_stack.md).
 GEMM_DRAM_TRAFFIC_PER_LAUNCH = 10274848
+# the same for the one launch of stack_u8s8_tcgen05_kernel (profiles/stack_u8s8_tcgen05_bert_stack.md); None
+# until captured
+STACK_DRAM_TRAFFIC_PER_LAUNCH = None
 
 
 def measured_peaks():
@@ -202,18 +207,24 @@ def run_b200_arm(args, rank, world, local_rank):
         torch.cuda.synchronize()
 
     # eager warm-up (also sets kernel attributes before any capture)
+    fused = args.fused
+    if fused:
+        stack.build_fused()
+    step_eager = stack.step_fused if fused else stack.step
+    # the dominant kernel alone: the 24 GEMMs, as one persistent kernel or as 24 launches
+    gemm_eager = (lambda: B.CHECK_STATUS(lib.bolt_b200_linear_stack_run(stack.plan))) if fused else stack.gemms
     for _ in range(max(args.warmup, 3)):
-        stack.step()
+        step_eager()
     torch.cuda.synchronize()
     launch_mode = "cuda_graph"
     g_step = g_gemm = None
     try:
         g_step = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g_step, stream=stream):
-            stack.step()
+            step_eager()
         g_gemm = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g_gemm, stream=stream):
-            stack.gemms()
+            gemm_eager()
         g_step.replay()
         g_gemm.replay()
         torch.cuda.synchronize()
@@ -232,8 +243,8 @@ def run_b200_arm(args, rank, world, local_rank):
         torch.cuda.synchronize()
         return sum(a.elapsed_time(b) for a, b in evs) / 1e3
 
-    step_fn = g_step.replay if g_step is not None else stack.step
-    gemm_fn = g_gemm.replay if g_gemm is not None else stack.gemms
+    step_fn = g_step.replay if g_step is not None else step_eager
+    gemm_fn = g_gemm.replay if g_gemm is not None else gemm_eager
     for _ in range(args.warmup):
         evict()
         step_fn()
@@ -248,13 +259,14 @@ def run_b200_arm(args, rank, world, local_rank):
     wall_s = time.perf_counter() - wall0
     launches = lib.bolt_b200_launch_count() - launches0
     if g_step is not None:
-        launches = stack.launches_per_step * args.steps  # replays re-launch the captured kernels
+        per_step = stack.launches_per_step_fused if fused else stack.launches_per_step
+        launches = per_step * args.steps  # replays re-launch the captured kernels
     clocks = sampler.stop() if rank == 0 else None
     # roofline pass: the GEMM launches alone
     gemm_s = timed(gemm_fn, args.steps)
     # end to end through the public host API
     for _ in range(2):
-        stack.run_host(x_host, out_host)
+        stack.run_host(x_host, out_host, fused)
     barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):
@@ -264,7 +276,7 @@ def run_b200_arm(args, rank, world, local_rank):
     t0 = time.perf_counter()
     for _ in range(args.steps):
         evict()
-        stack.run_host(x_host, out_host)
+        stack.run_host(x_host, out_host, fused)
     torch.cuda.synchronize()
     e2e_s = max(time.perf_counter() - t0 - flush_s, 1e-9)
     status = lib.bolt_b200_device_status()
@@ -282,7 +294,7 @@ def run_b200_arm(args, rank, world, local_rank):
     peaks, peak_src = measured_peaks()
     total_ops = OPS_PER_STEP * args.steps * world
     value = total_ops / dev_s / 1e12
-    n_gemm = 2 * LAYERS
+    n_gemm = 1 if fused else 2 * LAYERS
     gemm_tops = OPS_PER_STEP / (gemm_s / args.steps) / 1e12
     peak_i8 = 2.0 * peaks["bf16_tflops"]
     base, _ = cpu_stack_baseline(seconds=12.0) if (world == 1 and not args.no_cpu_baseline) else (None, None)
@@ -299,8 +311,10 @@ def run_b200_arm(args, rank, world, local_rank):
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": gemm_tops, "peak": peak_i8, "unit": "TFLOP/s",
-                     "frac": gemm_tops / peak_i8, "traffic": GEMM_DRAM_TRAFFIC_PER_LAUNCH,
-                     "kernel": "gemm_u8s8_tcgen05_kernel", "launches_per_step": n_gemm,
+                     "frac": gemm_tops / peak_i8,
+                     "traffic": STACK_DRAM_TRAFFIC_PER_LAUNCH if fused else GEMM_DRAM_TRAFFIC_PER_LAUNCH,
+                     "kernel": "stack_u8s8_tcgen05_kernel" if fused else "gemm_u8s8_tcgen05_kernel",
+                     "launches_per_step": n_gemm,
                      "us_per_launch": gemm_s / args.steps / n_gemm * 1e6,
                      "ops_per_launch": OPS_PER_STEP / n_gemm,
                      "note": "int8 multiply-add ops (2*M*N*K) in the TFLOP/s slot; peak = 2 x bf16_tflops of "
@@ -337,6 +351,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU leg (profiling runs)")
+    ap.add_argument("--fused", action="store_true",
+                    help="run the 24 GEMMs inside one persistent cooperative kernel instead of one launch per layer")
     ap.add_argument("--workload", default="bert_stack",
                     help="bert_stack (the headline, default) or one of the side workloads: ffn, gemv, quantize, "
                          "resnet_conv, bnn (1 GPU, prints that workload's figures as one JSON line)")

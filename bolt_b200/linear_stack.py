@@ -9,7 +9,7 @@ import ctypes as C
 
 import numpy as np
 
-from . import (CHECK_STATUS, DF_NORMAL, DF_TRANSPOSE, DT_F32, DT_I8, DT_I32, DT_U8_Q, GemmEpilogue, lib,
+from . import (CHECK_STATUS, DF_NORMAL, DF_TRANSPOSE, DT_F32, DT_I8, DT_I32, DT_U8_Q, GemmEpilogue, StackLayer, lib,
                matrix_matrix_multiply_transform_rhs, matrix_matrix_multiply_transform_rhs_bytes, tensor2df)
 
 
@@ -127,11 +127,63 @@ class LinearStack:
             sA, cur = so, 1 - cur
         torch.cuda.synchronize()
 
-    def run_host(self, x_host, out_host):
+    # ---- the whole stack as one persistent kernel ----------------------------------------------
+    def build_fused(self):
+        """Plan for bolt_b200_linear_stack_run (needs calibrate() first): per-channel conversion factors
+        of every layer -- layer 0's is recomputed each step from the dynamic input scale -- and the
+        tensor maps, encoded once."""
+        torch = _torch()
+        L = lib()
+        n = len(self.layers)
+        self.factors = [torch.zeros(l.N, dtype=torch.float32, device="cuda") for l in self.layers]
+        descs = (StackLayer * n)()
+        cur, sA = 0, None
+        for i, l in enumerate(self.layers):
+            last = i == n - 1
+            num = 1.0 if last else self.out_scales[i]
+            if i > 0:
+                cs = None if l.uniform else C.c_void_p(l.w_scale.data_ptr())
+                CHECK_STATUS(L.bolt_b200_col_factor(num, sA, None, float(l.w_scale_host[0]), cs, l.N,
+                                                    C.c_void_p(self.factors[i].data_ptr())), "col_factor")
+            descs[i].N, descs[i].K = l.N, l.K
+            descs[i].packedB = l.packed.data_ptr()
+            descs[i].offsetC = l.offsetC_ptr
+            descs[i].col_factor = self.factors[i].data_ptr()
+            descs[i].C = self.out_dev.data_ptr() if last else self.act[1 - cur].data_ptr()
+            descs[i].out_dt = DT_F32 if last else DT_U8_Q
+            if not last:
+                sA, cur = self.out_scales[i], 1 - cur
+        plan = C.c_void_p()
+        CHECK_STATUS(L.bolt_b200_linear_stack_plan(self.M, C.c_void_p(self.act[0].data_ptr()), descs, n, C.byref(plan)),
+                     "linear_stack_plan")
+        torch.cuda.synchronize()
+        self.plan = plan
+        self.launches_per_step_fused = 5  # absmax, scale, quantize, layer-0 factors, the stack kernel
+
+    def step_fused(self):
+        """One pass, device resident, every layer inside one kernel."""
+        L = lib()
+        l0 = self.layers[0]
+        self.quantize_input()
+        num0 = 1.0 if len(self.layers) == 1 else self.out_scales[0]
+        cs = None if l0.uniform else C.c_void_p(l0.w_scale.data_ptr())
+        CHECK_STATUS(L.bolt_b200_col_factor(num0, 1.0, C.c_void_p(self.d_scale.data_ptr()), float(l0.w_scale_host[0]), cs,
+                                            l0.N, C.c_void_p(self.factors[0].data_ptr())), "col_factor")
+        CHECK_STATUS(L.bolt_b200_linear_stack_run(self.plan), "linear_stack_run")
+
+    def free_fused(self):
+        if getattr(self, "plan", None):
+            lib().bolt_b200_linear_stack_free(self.plan)
+            self.plan = None
+
+    def run_host(self, x_host, out_host, fused=False):
         """End to end from pinned host memory: H2D of the fp32 input, one pass, D2H of the fp32 output."""
         torch = _torch()
         self.x_dev.copy_(x_host, non_blocking=True)
-        self.step()
+        if fused:
+            self.step_fused()
+        else:
+            self.step()
         out_host.copy_(self.out_dev, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
