@@ -56,8 +56,20 @@ __global__ void absmax_f32_kernel(const float *__restrict__ x, uint64_t n, unsig
     for (int o = 16; o > 0; o >>= 1) {
         m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
     }
-    if ((threadIdx.x & 31) == 0 && m != 0) {
-        atomicMax(out_bits, m);
+    // one atomic per CTA: thousands of warps hitting one address serialise in L2
+    __shared__ unsigned warp_max[TPB / 32];
+    if ((threadIdx.x & 31) == 0) {
+        warp_max[threadIdx.x >> 5] = m;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int w = 1; w < TPB / 32; ++w) {
+            m = max(m, warp_max[w]);
+        }
+        if (m != 0) {
+            atomicMax(out_bits, m);
+        }
     }
 }
 
@@ -85,8 +97,19 @@ __global__ void absmax_i32_kernel(const int32_t *__restrict__ x, uint64_t n, int
     for (int o = 16; o > 0; o >>= 1) {
         m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
     }
-    if ((threadIdx.x & 31) == 0 && m != 0) {
-        atomicMax(out, m);
+    __shared__ int warp_max[TPB / 32];
+    if ((threadIdx.x & 31) == 0) {
+        warp_max[threadIdx.x >> 5] = m;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int w = 1; w < TPB / 32; ++w) {
+            m = max(m, warp_max[w]);
+        }
+        if (m != 0) {
+            atomicMax(out, m);
+        }
     }
 }
 
