@@ -95,7 +95,7 @@ class GemmEpilogue(C.Structure):
     """bolt_b200_gemm_epilogue"""
     _fields_ = [("out_dt", C.c_uint32), ("accumulate", C.c_int), ("out_scale", C.c_float),
                 ("sA", C.c_float), ("sB", C.c_float), ("d_sA", C.c_void_p),
-                ("row_scale", C.c_void_p), ("col_scale", C.c_void_p)]
+                ("row_scale", C.c_void_p), ("col_scale", C.c_void_p), ("col_factor", C.c_void_p)]
 
 
 class StackLayer(C.Structure):

@@ -301,6 +301,10 @@ EE bolt_b200_gemm_u8s8_ex(U32 N, U32 M, U32 K, const void *A, const void *packed
     ep.sA_dev = e->d_sA;
     ep.row_scale = e->row_scale;
     ep.col_scale = e->col_scale;
+    ep.col_factor = e->col_factor;
+    if (e->col_factor != nullptr && e->row_scale != nullptr) {
+        return NOT_SUPPORTED;
+    }
     return run_gemm(N, M, K, false, A, packedB, offsetC, C, ep);
 }
 

@@ -153,6 +153,7 @@ struct GemmEpilogue {
     const float *sA_dev;       // device scalar overriding sA, or null
     const float *row_scale;    // [M] or null
     const float *col_scale;    // [N] or null
+    const float *col_factor;   // [N] or null: ready-made per-column factors (then nothing is divided in the kernel)
 };
 
 // B: ALIGN(N,16) rows, pitch Kp = ALIGN(K,8) bytes, K contiguous, zero padded.

@@ -124,7 +124,9 @@ __global__ void gemm_simt_kernel(uint32_t M, uint32_t N, uint32_t K, const uint8
         return;
     }
     float fac = ep.factor;
-    if (ep.per_channel) {
+    if (ep.col_factor != nullptr) {
+        fac = ep.col_factor[n];
+    } else if (ep.per_channel) {
         const float sa_ = ep.row_scale ? ep.row_scale[m] : (ep.sA_dev ? *ep.sA_dev : ep.sA);
         const float sb_ = ep.col_scale ? ep.col_scale[n] : ep.sB;
         fac = __fdiv_rn(ep.num, __fmul_rn(sa_, sb_));

@@ -400,7 +400,9 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     if (ep.offsetC != nullptr) {
                         asm volatile("ld.global.nc.b32 %0, [%1];" : "=r"(o[q]) : "l"(ep.offsetC + n));
                     }
-                    if (ep.per_channel && ep.col_scale != nullptr) {
+                    if (ep.col_factor != nullptr) {
+                        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(sb[q]) : "l"(ep.col_factor + n));
+                    } else if (ep.per_channel && ep.col_scale != nullptr) {
                         asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(sb[q]) : "l"(ep.col_scale + n));
                     }
                 }
@@ -411,6 +413,9 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(sa_dev) : "l"(ep.sA_dev));
         }
         auto factor_of = [&](float sb) {
+            if (ep.col_factor != nullptr) {
+                return sb;  // already the factor
+            }
             if (!ep.per_channel) {
                 return ep.factor;
             }

@@ -72,8 +72,9 @@ class LinearStack:
         self.launches_per_step = 3 + len(layers)
 
     # ---- pieces -------------------------------------------------------------------------
-    def _gemm(self, l, a_ptr, c_ptr, out_dt, out_scale, sA, d_sA=None):
+    def _gemm(self, l, a_ptr, c_ptr, out_dt, out_scale, sA, d_sA=None, factor=None):
         ep = GemmEpilogue()
+        ep.col_factor = None if factor is None else C.c_void_p(factor.data_ptr())
         ep.out_dt, ep.accumulate, ep.out_scale = out_dt, 0, float(out_scale)
         ep.sA, ep.sB = float(sA), float(l.w_scale_host[0])
         ep.d_sA = d_sA
@@ -94,11 +95,13 @@ class LinearStack:
         cur = 0
         sA, d_sA = 1.0, C.c_void_p(self.d_scale.data_ptr())
         last = len(self.layers) - 1
+        fac = getattr(self, "layer_factors", None)
         for i, l in enumerate(self.layers):
+            f = fac[i] if (fac is not None and i > 0) else None  # layer 0 divides by the dynamic input scale
             if i == last:
-                self._gemm(l, self.act[cur].data_ptr(), self.out_dev.data_ptr(), DT_F32, 1.0, sA, d_sA)
+                self._gemm(l, self.act[cur].data_ptr(), self.out_dev.data_ptr(), DT_F32, 1.0, sA, d_sA, f)
             else:
-                self._gemm(l, self.act[cur].data_ptr(), self.act[1 - cur].data_ptr(), DT_U8_Q, self.out_scales[i], sA, d_sA)
+                self._gemm(l, self.act[cur].data_ptr(), self.act[1 - cur].data_ptr(), DT_U8_Q, self.out_scales[i], sA, d_sA, f)
                 sA, d_sA = self.out_scales[i], None
                 cur = 1 - cur
 
@@ -125,6 +128,26 @@ class LinearStack:
             self.out_scales[i] = so
             self._gemm(l, self.act[cur].data_ptr(), self.act[1 - cur].data_ptr(), DT_U8_Q, so, sA)
             sA, cur = so, 1 - cur
+        torch.cuda.synchronize()
+        self._build_factors()
+
+    def _build_factors(self):
+        """Per-channel conversion factors of layers 1.. (their input scales are calibrated constants):
+        num / (sA * sB[n]) once, instead of a division per column per tile inside the kernels."""
+        torch = _torch()
+        L = lib()
+        n = len(self.layers)
+        self.layer_factors = [torch.zeros(l.N, dtype=torch.float32, device="cuda") for l in self.layers]
+        sA = None
+        for i, l in enumerate(self.layers):
+            last = i == n - 1
+            num = 1.0 if last else self.out_scales[i]
+            if i > 0:
+                cs = None if l.uniform else C.c_void_p(l.w_scale.data_ptr())
+                CHECK_STATUS(L.bolt_b200_col_factor(num, sA, None, float(l.w_scale_host[0]), cs, l.N,
+                                                    C.c_void_p(self.layer_factors[i].data_ptr())), "col_factor")
+            if not last:
+                sA = self.out_scales[i]
         torch.cuda.synchronize()
 
     # ---- the whole stack as one persistent kernel ----------------------------------------------

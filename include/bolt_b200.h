@@ -249,6 +249,8 @@ typedef struct {
     const F32 *d_sA;      /* device scalar overriding sA (e.g. from bolt_b200_absmax_scale_f32) */
     const F32 *row_scale; /* device [M], overrides sA / d_sA */
     const F32 *col_scale; /* device [N], overrides sB */
+    const F32 *col_factor; /* device [N]: ready-made conversion factors (bolt_b200_col_factor); when set,
+                              out_scale, sA, sB, d_sA and col_scale are not used (row_scale must be NULL) */
 } bolt_b200_gemm_epilogue;
 EE bolt_b200_gemm_u8s8_ex(U32 N, U32 M, U32 K, const void *A, const void *packedB,
     const I32 *offsetC, void *C, const bolt_b200_gemm_epilogue *ep);
