@@ -314,6 +314,15 @@ EE matrix_vector_multiply_transform_weight_bytes_cuda_b200(U32 row, U32 col, Dat
     if (bytes == nullptr) {
         return NULL_POINTER;
     }
+    if (dt == DT_U8_Q) {
+        // the u8 matrix x s8 vector form needs no packing here; the reference's counts are kept so that
+        // callers size tmp the same way (cpu/x86/mvm.cpp:30-40)
+        *bytes = (col % 32 != 0) ? 32 * (row + 1) : 0;
+        if (df != DF_NK) {
+            *bytes += B200_ALIGN(row, 16) * B200_ALIGN(col, 8) + 32;
+        }
+        return SUCCESS;
+    }
     if (dt != DT_I8) {
         return NOT_SUPPORTED;
     }
@@ -364,12 +373,37 @@ EE matrix_vector_multiply_tmp_bytes_cuda_b200(U32 row, U32 col, DataType dt, Dat
 EE mvm_cuda_b200(U32 row, U32 col, DataType dt, DataFormat df, const void *matrix, const void *vector,
     void *result, void *offsetCBias, const F32 *scale)
 {
-    (void)df;
-    if (dt != DT_I8) {
+    if (dt != DT_I8 && dt != DT_U8_Q) {
         return NOT_SUPPORTED;
     }
     if (offsetCBias == nullptr) {
-        return NULL_POINTER;  // CHECK_REQUIREMENT(offsetCBias != nullptr), cpu/x86/mvm.cpp:119
+        return NULL_POINTER;  // CHECK_REQUIREMENT(offsetCBias != nullptr), cpu/x86/mvm.cpp:119,126
+    }
+    if (dt == DT_U8_Q) {
+        // u8 matrix x s8 vector (mvm_avx512_int8_row_i8u8): the offset is -128 * sum(vector), found per call
+        if (df != DF_NORMAL && df != DF_TRANSPOSE) {
+            return NOT_SUPPORTED;
+        }
+        if (ctx() == nullptr) {
+            return UNKNOWN;
+        }
+        if (row == 0) {
+            return SUCCESS;
+        }
+        if (matrix == nullptr || vector == nullptr || result == nullptr) {
+            return NULL_POINTER;
+        }
+        GemmEpilogue ep;
+        scale_to_epilogue(scale, &ep);
+        Stage sg;
+        const uint8_t *dM = reinterpret_cast<const uint8_t *>(sg.in(matrix, (size_t)row * col));
+        const int8_t *dv = reinterpret_cast<const int8_t *>(sg.in(vector, col));
+        void *dy = sg.out(result, (size_t)row * (ep.out_kind == 2 ? 1 : 4));
+        if (dM == nullptr || dv == nullptr || dy == nullptr) {
+            return ALLOC_FAILED;
+        }
+        B200_EE(launch_gemv_row(row, col, dM, df == DF_TRANSPOSE, dv, dy, ep.out_kind, ep.factor, tls().stream));
+        return sg.finish();
     }
     DeviceCtx *c = ctx();
     if (c == nullptr) {
@@ -573,7 +607,7 @@ EE b200_matrix_vector_multiply(TensorDesc mDesc, const void *matrix, TensorDesc 
     if (arch != CUDA_B200) {
         return NOT_SUPPORTED;
     }
-    if (mdt != DT_I8 || vdt != DT_U8_Q) {
+    if (!((mdt == DT_I8 && vdt == DT_U8_Q) || (mdt == DT_U8_Q && vdt == DT_I8))) {
         return NOT_SUPPORTED;
     }
     if (tmp == nullptr) {
@@ -581,6 +615,12 @@ EE b200_matrix_vector_multiply(TensorDesc mDesc, const void *matrix, TensorDesc 
     }
     if (rdt == DT_I32) {
         scale = nullptr;
+    }
+    if (mdt == DT_U8_Q) {
+        if (mdf == DF_NK) {
+            return NOT_SUPPORTED;  // mvm.cpp:170-173
+        }
+        return mvm_cuda_b200(row, col, mdt, mdf, matrix, vector, result, tmp, scale);
     }
     const void *dataB = matrix;
     if (mdf != DF_NKN32K4) {

@@ -165,6 +165,8 @@ EE launch_gemm_simt(uint32_t M, uint32_t N, uint32_t K, const uint8_t *A, bool a
     const int8_t *B, uint32_t Kp, void *C, const GemmEpilogue &ep, cudaStream_t st);
 EE launch_pack_rhs(const int8_t *src, bool src_is_nk, uint32_t N, uint32_t K, int8_t *dst,
     uint32_t Kp, uint32_t Np, int32_t *offsetC, cudaStream_t st);
+EE launch_gemv_row(uint32_t N, uint32_t K, const uint8_t *Mx, bool transposed, const int8_t *v, void *y, int out_kind,
+    float factor, cudaStream_t st);
 EE launch_gemv(uint32_t N, uint32_t K, const int8_t *W, uint32_t Kp, const uint8_t *x,
     const int32_t *offsetC, void *y, int out_kind, float factor, cudaStream_t st);
 

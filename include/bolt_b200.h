@@ -299,7 +299,12 @@ EE matrix_vector_multiply_transform_weight_cuda_b200(const TensorDesc *desc, con
 EE matrix_vector_multiply_tmp_bytes_cuda_b200(U32 row, U32 col, DataType dt, DataFormat df, U32 *bytes);
 /* replaces cpu/x86/mvm.cpp:102-138 (mvm_x86 -> mvm_avx512_int8, mvm_avx512_vnni.cpp:703-759).
  * Same three output modes as mmm_cuda_b200.  The last N%8 rows follow the reference's scalar
- * tail (mvm_avx512_vnni.cpp:667-701): incoming y ignored, u8 = min(255, trunc(f + 128)). */
+ * tail (mvm_avx512_vnni.cpp:667-701): incoming y ignored, u8 = min(255, trunc(f + 128)).
+ * dt == DT_U8_Q selects the other operand order, a u8 matrix ([N,K] DF_NORMAL or [K,N]
+ * DF_TRANSPOSE, not packed) times an s8 vector -- mvm_avx512_int8_row_i8u8,
+ * mvm_avx512_vnni_row.cpp:931-1028, what Bolt's matmul uses for vector outputs (matmul.cpp:376-379):
+ * y = -128*sum(vector) + M*v, y is only written; the last N%4 rows use the single-row kernel's u8
+ * store (low byte of rne + 128 unless that is >= 255).  offsetCBias must be non-NULL, it is not read. */
 EE mvm_cuda_b200(U32 row, U32 col, DataType dt, DataFormat df, const void *matrix,
     const void *vector, void *result, void *offsetCBias, const F32 *scale);
 

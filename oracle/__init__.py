@@ -78,6 +78,7 @@ def _load_port():
     lib.oracle_offsetc.argtypes = [_vp, _u32, _u32, _i32, _vp]
     lib.oracle_gemm_u8s8.argtypes = [_u32, _u32, _u32, _vp, _i32, _vp, _i32, _vp, _vp, _vp]
     lib.oracle_gemv_s8u8.argtypes = [_u32, _u32, _vp, _i32, _vp, _vp, _vp, _vp]
+    lib.oracle_gemv_u8s8_row.argtypes = [_u32, _u32, _vp, _i32, _vp, _vp, _vp]
     lib.oracle_scale_f32.restype = _c.c_float
     lib.oracle_scale_f32.argtypes = [_vp, _u64]
     lib.oracle_scale_i32.restype = _c.c_float
@@ -123,6 +124,7 @@ def _load_ref():
     lib.ref_gemv_plan.argtypes = [_u32, _u32, _i32, _vp, _i32]
     lib.ref_gemv_run.argtypes = [_vp, _vp, _vp, _vp, _vp]
     lib.ref_gemv_free.argtypes = [_vp]
+    lib.ref_gemv_row.argtypes = [_u32, _u32, _i32, _vp, _vp, _vp, _i32, _vp]
     lib.ref_quantize.argtypes = [_u32, _i32, _vp, _i32, _vp, _vp, _i32]
     lib.ref_dequantize.argtypes = [_u32, _i32, _vp, _vp, _vp]
     lib.ref_bias_offsetc.argtypes = [_u32, _vp, _vp, _c.c_float, _vp]
@@ -208,3 +210,22 @@ def ref_gemv(W, x, scale=None, y_in=None, w_t=False, offsetC=None):
     ref.ref_gemv_free(pl)
     assert rc == 0
     return y
+
+
+def port_gemv_row(Mx, v, scale=None, m_t=False):
+    """Mx u8 [N,K] (or [K,N] if m_t), v s8 [K]"""
+    N, K = Mx.shape[::-1] if m_t else Mx.shape
+    y = np.zeros(N, _OUT_DT[out_kind(scale)])
+    s = _scale_arr(scale)
+    port.oracle_gemv_u8s8_row(N, K, ptr(Mx), int(m_t), ptr(v), ptr(y), ptr(s))
+    return y
+
+
+def ref_gemv_row(Mx, v, scale=None, m_t=False):
+    N, K = Mx.shape[::-1] if m_t else Mx.shape
+    kind = out_kind(scale)
+    y = np.zeros(N + 64, _OUT_DT[kind])
+    s = _scale_arr(scale)
+    rc = ref.ref_gemv_row(N, K, int(m_t), ptr(Mx), ptr(v), ptr(y), kind, ptr(s))
+    assert rc == 0
+    return y[:N].copy()

@@ -153,6 +153,49 @@ void oracle_gemv_s8u8(uint32_t N, uint32_t K, const int8_t *W, int w_transposed,
     }
 }
 
+/* mvm_avx512_vnni_row.cpp:931-1028 (driver: offset = -128 * sum of the vector, :940-983; rows in
+ * groups of 16 / 8 / 4, the rest one by one, :1012-1024), :384-406, :632-640, :786-791 (vpmovusdb
+ * in the multi-row kernels) and :884-900 (single-row kernel: add 128, signed compare with 255,
+ * low byte stored).  The result buffer is only written, never read. */
+void oracle_gemv_u8s8_row(uint32_t N, uint32_t K, const uint8_t *Mx, int m_transposed, const int8_t *v,
+    void *y, const float *scale)
+{
+    int mode = 0;
+    float factor = 0;
+    if (scale != NULL) {
+        if (scale[0] < 0) {
+            mode = 2;
+            factor = scale[1];
+        } else {
+            mode = 1;
+            factor = 1 / scale[0];
+        }
+    }
+    int32_t off = 0;
+    for (uint32_t k = 0; k < K; ++k) {
+        off += v[k];
+    }
+    off *= -128;
+    uint32_t single_begin = N - (N % 4);
+    for (uint32_t n = 0; n < N; ++n) {
+        int32_t acc = off;
+        for (uint32_t k = 0; k < K; ++k) {
+            int32_t m = m_transposed ? Mx[(size_t)k * N + n] : Mx[(size_t)n * K + k];
+            acc += m * (int32_t)v[k];
+        }
+        if (mode == 0) {
+            ((int32_t *)y)[n] = acc;
+        } else if (mode == 1) {
+            ((float *)y)[n] = (float)acc * factor;
+        } else if (n >= single_begin) {
+            int32_t t = (int32_t)((uint32_t)oracle_cvt_rne((float)acc * factor) + 128u);
+            ((uint8_t *)y)[n] = (t < 255) ? (uint8_t)t : 255;
+        } else {
+            ((uint8_t *)y)[n] = acc_to_u8(acc, factor);
+        }
+    }
+}
+
 /* ------------------------------------------------------------------------------ */
 /* quantize / dequantize                                                          */
 /* ------------------------------------------------------------------------------ */

@@ -44,6 +44,12 @@ void oracle_gemm_u8s8(uint32_t M, uint32_t N, uint32_t K, const uint8_t *A, int 
 void oracle_gemv_s8u8(uint32_t N, uint32_t K, const int8_t *W, int w_transposed,
     const uint8_t *x, const int32_t *offsetC, void *y, const float *scale);
 
+/* y = epilogue( -128 * sum_k v[k] + sum_k M_u8[n,k] * v_s8[k] ), M stored [N,K] (m_transposed: [K,N]).
+ * The incoming y is never added.  Same scale protocol; the last N%4 rows follow the reference's
+ * single-row kernel, whose u8 store keeps the low byte of (rne + 128) unless that sum is >= 255. */
+void oracle_gemv_u8s8_row(uint32_t N, uint32_t K, const uint8_t *Mx, int m_transposed, const int8_t *v,
+    void *y, const float *scale);
+
 /* ---- quantize / dequantize (compute/tensor) -------------------------------------- */
 float oracle_scale_f32(const float *x, uint64_t n);      /* 127/absmax, 1 if absmax==0 */
 float oracle_scale_i32(const int32_t *x, uint64_t n);    /* 127.0f/(float)max|x| */

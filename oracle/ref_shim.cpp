@@ -197,6 +197,25 @@ void ref_gemv_free(RefGemvPlan *pl)
     }
 }
 
+// u8 matrix x s8 vector (the GEMV Bolt's matmul uses when the output is a vector, matmul.cpp:376-379).
+// Mx: u8 [N,K] (transM=0) or [K,N] (transM=1).
+int ref_gemv_row(uint32_t N, uint32_t K, int transM, const uint8_t *Mx, const int8_t *v, void *y, int out_kind,
+    const float *scale)
+{
+    TensorDesc mDesc = transM ? tensor2df(DT_U8_Q, DF_TRANSPOSE, K, N) : tensor2df(DT_U8_Q, DF_NORMAL, N, K);
+    TensorDesc vDesc = tensor1d(DT_I8, K);
+    TensorDesc yDesc = tensor1d(c_dtype(out_kind), N);
+    U32 bytes = 0;
+    matrix_vector_multiply_tmp_bytes(mDesc, vDesc, &bytes, X86_AVX512);
+    Buf tmp((size_t)bytes + (size_t)N * K + (size_t)N * 8 + 256);
+    Buf mcopy((size_t)N * K + 256);  // the kernels read whole 64-byte vectors: keep slack behind the matrix
+    memcpy(mcopy.p, Mx, (size_t)N * K);
+    Buf vcopy((size_t)K + 256);
+    memcpy(vcopy.p, v, K);
+    return (int)matrix_vector_multiply(mDesc, mcopy.p, vDesc, vcopy.p, bytes + N * K + N * 8, tmp.p, yDesc, y, scale,
+        X86_AVX512);
+}
+
 // ---- quantize / dequantize ---------------------------------------------------------
 // src_kind / dst_kind use Bolt DataType numbers (DT_F32=6, DT_I32=3, DT_U8_Q=10, DT_I8=1).
 int ref_quantize(uint32_t n, int src_dt, const void *src, int dst_dt, void *dst, float *scale, int mode)

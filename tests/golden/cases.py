@@ -87,3 +87,14 @@ def conv_variants(i):
     ic = CONV_SHAPES[i][1]
     blocks = (8, 16) if ic % 16 == 0 else (8,)
     return [(b, u, r) for b in blocks for u in (0, 1) for r in (0, 1)]
+
+
+GEMV_ROW_SHAPES = [(1, 1), (3, 5), (4, 16), (7, 33), (17, 64), (33, 130), (64, 256), (67, 1000)]
+
+
+def gemv_row_inputs(i, m_t):
+    n, k = GEMV_ROW_SHAPES[i]
+    seed = 9000 + i * 2 + m_t
+    Mx = synth.u8(seed, (k, n) if m_t else (n, k))
+    v = synth.s8(seed + 500, (k,))
+    return Mx, v

@@ -106,12 +106,25 @@ def conv_outputs():
     return out
 
 
+def gemv_row_outputs():
+    out = {}
+    for i in range(len(cases.GEMV_ROW_SHAPES)):
+        for m_t in (0, 1):
+            Mx, v = cases.gemv_row_inputs(i, m_t)
+            key = "r%d_%d" % (i, m_t)
+            out[key + "_s32"] = O.ref_gemv_row(Mx, v, None, m_t)
+            out[key + "_f32"] = O.ref_gemv_row(Mx, v, cases.GEMM_F32_SCALE, m_t)
+            out[key + "_u8"] = O.ref_gemv_row(Mx, v, cases.GEMM_U8_SCALE, m_t)
+    return out
+
+
 def main():
+    np.savez_compressed(os.path.join(HERE, "gemv_row.npz"), **gemv_row_outputs())
     np.savez_compressed(os.path.join(HERE, "conv.npz"), **conv_outputs())
     np.savez_compressed(os.path.join(HERE, "gemm.npz"), **gemm_outputs())
     np.savez_compressed(os.path.join(HERE, "gemv.npz"), **gemv_outputs())
     np.savez_compressed(os.path.join(HERE, "quantize.npz"), **quant_outputs())
-    for f in ("gemm.npz", "gemv.npz", "quantize.npz", "conv.npz"):
+    for f in ("gemm.npz", "gemv.npz", "gemv_row.npz", "quantize.npz", "conv.npz"):
         print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
 
 

@@ -345,3 +345,45 @@ def test_mvm_large_vs_oracle():
     off = O.port_offsetc(W, True)
     for sc in (None, [0.37], [-1, 0.0004]):
         assert same_bits(mvm_gpu(W, x, sc), O.port_gemv(W, x, off, sc)), sc
+
+
+# ------------------------------------------------------- u8 matrix x s8 vector (matmul's GEMV)
+def mvm_row_gpu(Mx, v, scale=None, m_t=False, host=False):
+    n, k = Mx.shape[::-1] if m_t else Mx.shape
+    m_desc = B.tensor2df(B.DT_U8_Q, B.DF_TRANSPOSE, k, n) if m_t else B.tensor2df(B.DT_U8_Q, B.DF_NORMAL, n, k)
+    v_desc = B.tensor1d(B.DT_I8, k)
+    rdt = out_dt(scale)
+    r_desc = B.tensor1d(rdt, n)
+    npdt = NP_OF[rdt]
+    nbt = B.matrix_vector_multiply_tmp_bytes(m_desc, v_desc)
+    if host:
+        y, tmp = np.zeros(n, npdt), np.zeros(nbt + 64, np.uint8)
+        B.matrix_vector_multiply(m_desc, hptr(Mx), v_desc, hptr(v), nbt, hptr(tmp), r_desc, hptr(y), scale)
+        return y
+    dM, dv, dy, tmp = to_dev(Mx), to_dev(v), dev_zeros(n * 4), dev_zeros(nbt + 64)
+    B.matrix_vector_multiply(m_desc, dptr(dM), v_desc, dptr(dv), nbt, dptr(tmp), r_desc, dptr(dy), scale)
+    B.CHECK_STATUS(B.lib().bolt_b200_synchronize(), "synchronize")
+    return to_host(dy, npdt, n)
+
+
+def test_mvm_row_golden_and_sweep():
+    g = np.load(os.path.join(GOLD, "gemv_row.npz"))
+    for i in range(len(cases.GEMV_ROW_SHAPES)):
+        for m_t in (0, 1):
+            Mx, v = cases.gemv_row_inputs(i, m_t)
+            key = "r%d_%d" % (i, m_t)
+            assert same_bits(mvm_row_gpu(Mx, v, None, m_t), g[key + "_s32"]), key
+            assert same_bits(mvm_row_gpu(Mx, v, cases.GEMM_F32_SCALE, m_t), g[key + "_f32"]), key
+            assert same_bits(mvm_row_gpu(Mx, v, cases.GEMM_U8_SCALE, m_t), g[key + "_u8"]), key
+    Mx, v = cases.gemv_row_inputs(5, 0)
+    assert same_bits(mvm_row_gpu(Mx, v, None, host=True), g["r5_0_s32"])
+    bad = []
+    for n, k in itertools.product([1, 2, 5, 8, 13, 16, 33, 64, 65], [1, 4, 15, 16, 48, 100, 512]):
+        for m_t in (0, 1):
+            Mx, v = synth.u8(n * 977 + k, (k, n) if m_t else (n, k)), synth.s8(n * 31 + k, (k,))
+            for sc in (None, [0.37], [-1, 0.002], [-1, 0.05]):
+                if not same_bits(mvm_row_gpu(Mx, v, sc, m_t), O.port_gemv_row(Mx, v, sc, m_t)):
+                    bad.append((n, k, m_t, sc))
+    assert not bad, bad[:10]
+    Mx, v = synth.u8(1, (2048, 4096)), synth.s8(2, (4096,))
+    assert same_bits(mvm_row_gpu(Mx, v, [-1, 0.0005]), O.port_gemv_row(Mx, v, [-1, 0.0005]))

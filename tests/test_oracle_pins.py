@@ -52,6 +52,17 @@ def test_golden_gemv():
             assert same_bits(O.port_gemv(W, x, off, cases.GEMM_U8_SCALE, None, w_t), g[key + "_u8"]), key
 
 
+def test_golden_gemv_row():
+    g = np.load(os.path.join(GOLD, "gemv_row.npz"))
+    for i in range(len(cases.GEMV_ROW_SHAPES)):
+        for m_t in (0, 1):
+            Mx, v = cases.gemv_row_inputs(i, m_t)
+            key = "r%d_%d" % (i, m_t)
+            assert same_bits(O.port_gemv_row(Mx, v, None, m_t), g[key + "_s32"]), key
+            assert same_bits(O.port_gemv_row(Mx, v, cases.GEMM_F32_SCALE, m_t), g[key + "_f32"]), key
+            assert same_bits(O.port_gemv_row(Mx, v, cases.GEMM_U8_SCALE, m_t), g[key + "_u8"]), key
+
+
 def port_quant(kind, src, dst_dtype, scale, mode=0):
     n = src.size
     q = np.zeros(n, dst_dtype)
