@@ -9,8 +9,7 @@ weight scales and fused requantization to u8 between layers, fp32 output.  Synth
 
 `value`  : int8 GEMM TOP/s (2*M*N*K ops of the 24 GEMMs) with the input resident in HBM,
            the whole step replayed as one CUDA graph, L2 flushed between timed steps.  One GEMM launch
-           per layer by default; --fused runs the 24 GEMMs inside one persistent cooperative kernel
-           (bolt_b200_linear_stack_run), which measures the same on B200.
+           per layer.
 `e2e`    : the same metric through LinearStack.run_host: pinned host input -> H2D -> step -> D2H.
 `roofline`: the tcgen05 GEMM kernel alone (24 launches per pass) against 2 x the measured bf16 peak.
 `cpu_baseline` / --impl reference: the reference's own x86 AVX512-VNNI code (or the scalar oracle
@@ -36,9 +35,6 @@ WORKLOAD = "bert_base_int8_linear_stack: 12 x (768->3072->768), M=4096 tokens, s
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of gemm_u8s8_tcgen05_kernel, averaged over
 # the 24 launches of one pass (profiles/gemm_u8s8_tcgen05_bert_stack.md).
 GEMM_DRAM_TRAFFIC_PER_LAUNCH = 10274848
-# the same for the one launch of stack_u8s8_tcgen05_kernel (profiles/stack_u8s8_tcgen05_bert_stack.md); None
-# until captured
-STACK_DRAM_TRAFFIC_PER_LAUNCH = None
 
 
 def measured_peaks():
@@ -207,12 +203,8 @@ def run_b200_arm(args, rank, world, local_rank):
         torch.cuda.synchronize()
 
     # eager warm-up (also sets kernel attributes before any capture)
-    fused = args.fused
-    if fused:
-        stack.build_fused()
-    step_eager = stack.step_fused if fused else stack.step
-    # the dominant kernel alone: the 24 GEMMs, as one persistent kernel or as 24 launches
-    gemm_eager = (lambda: B.CHECK_STATUS(lib.bolt_b200_linear_stack_run(stack.plan))) if fused else stack.gemms
+    step_eager = stack.step
+    gemm_eager = stack.gemms  # the dominant kernel alone: the 24 GEMM launches
     for _ in range(max(args.warmup, 3)):
         step_eager()
     torch.cuda.synchronize()
@@ -259,13 +251,12 @@ def run_b200_arm(args, rank, world, local_rank):
     wall_s = time.perf_counter() - wall0
     launches = lib.bolt_b200_launch_count() - launches0
     if g_step is not None:
-        per_step = stack.launches_per_step_fused if fused else stack.launches_per_step
-        launches = per_step * args.steps  # replays re-launch the captured kernels
+        launches = stack.launches_per_step * args.steps  # replays re-launch the captured kernels
     # roofline pass: the GEMM launches alone
     gemm_s = timed(gemm_fn, args.steps)
     # end to end through the public host API
     for _ in range(2):
-        stack.run_host(x_host, out_host, fused)
+        stack.run_host(x_host, out_host)
     barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):
@@ -275,7 +266,7 @@ def run_b200_arm(args, rank, world, local_rank):
     t0 = time.perf_counter()
     for _ in range(args.steps):
         evict()
-        stack.run_host(x_host, out_host, fused)
+        stack.run_host(x_host, out_host)
     torch.cuda.synchronize()
     e2e_s = max(time.perf_counter() - t0 - flush_s, 1e-9)
     clocks = sampler.stop() if rank == 0 else None
@@ -294,7 +285,7 @@ def run_b200_arm(args, rank, world, local_rank):
     peaks, peak_src = measured_peaks()
     total_ops = OPS_PER_STEP * args.steps * world
     value = total_ops / dev_s / 1e12
-    n_gemm = 1 if fused else 2 * LAYERS
+    n_gemm = 2 * LAYERS
     gemm_tops = OPS_PER_STEP / (gemm_s / args.steps) / 1e12
     peak_i8 = 2.0 * peaks["bf16_tflops"]
     base, _ = cpu_stack_baseline(seconds=12.0) if (world == 1 and not args.no_cpu_baseline) else (None, None)
@@ -312,8 +303,8 @@ def run_b200_arm(args, rank, world, local_rank):
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": gemm_tops, "peak": peak_i8, "unit": "TFLOP/s",
                      "frac": gemm_tops / peak_i8,
-                     "traffic": STACK_DRAM_TRAFFIC_PER_LAUNCH if fused else GEMM_DRAM_TRAFFIC_PER_LAUNCH,
-                     "kernel": "stack_u8s8_tcgen05_kernel" if fused else "gemm_u8s8_tcgen05_kernel",
+                     "traffic": GEMM_DRAM_TRAFFIC_PER_LAUNCH,
+                     "kernel": "gemm_u8s8_tcgen05_kernel",
                      "launches_per_step": n_gemm,
                      "us_per_launch": gemm_s / args.steps / n_gemm * 1e6,
                      "ops_per_launch": OPS_PER_STEP / n_gemm,
@@ -351,8 +342,6 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU leg (profiling runs)")
-    ap.add_argument("--fused", action="store_true",
-                    help="run the 24 GEMMs inside one persistent cooperative kernel instead of one launch per layer")
     ap.add_argument("--workload", default="bert_stack",
                     help="bert_stack (the headline, default) or one of the side workloads: ffn, gemv, quantize, "
                          "resnet_conv, bnn (1 GPU, prints that workload's figures as one JSON line)")

@@ -95,13 +95,8 @@ class GemmEpilogue(C.Structure):
     """bolt_b200_gemm_epilogue"""
     _fields_ = [("out_dt", C.c_uint32), ("accumulate", C.c_int), ("out_scale", C.c_float),
                 ("sA", C.c_float), ("sB", C.c_float), ("d_sA", C.c_void_p),
-                ("row_scale", C.c_void_p), ("col_scale", C.c_void_p), ("col_factor", C.c_void_p)]
-
-
-class StackLayer(C.Structure):
-    """bolt_b200_stack_layer"""
-    _fields_ = [("N", C.c_uint32), ("K", C.c_uint32), ("packedB", C.c_void_p), ("offsetC", C.c_void_p),
-                ("col_factor", C.c_void_p), ("C", C.c_void_p), ("out_dt", C.c_uint32)]
+                ("row_scale", C.c_void_p), ("col_scale", C.c_void_p), ("col_factor", C.c_void_p),
+                ("prefetch", C.c_void_p), ("prefetch_bytes", C.c_size_t)]
 
 
 _vp, _u32, _u32p, _f32p = C.c_void_p, C.c_uint32, C.POINTER(C.c_uint32), C.POINTER(C.c_float)
@@ -127,9 +122,6 @@ SIGNATURES = {
     "mmm_cuda_b200": (C.c_int, [_u32, _u32, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _f32p]),
     "bolt_b200_gemm_u8s8_ex": (C.c_int, [_u32, _u32, _u32, _vp, _vp, _vp, _vp, C.POINTER(GemmEpilogue)]),
     "bolt_b200_quantize_f32_u8_dev": (C.c_int, [_vp, C.c_uint64, _vp, _vp]),
-    "bolt_b200_linear_stack_plan": (C.c_int, [_u32, _vp, C.POINTER(StackLayer), _u32, C.POINTER(C.c_void_p)]),
-    "bolt_b200_linear_stack_run": (C.c_int, [_vp]),
-    "bolt_b200_linear_stack_free": (C.c_int, [_vp]),
     "bolt_b200_col_factor": (C.c_int, [C.c_float, C.c_float, _vp, C.c_float, _vp, _u32, _vp]),
     "matrix_vector_multiply_transform_weight_bytes_cuda_b200": (C.c_int, [_u32, _u32, _u32, _u32, _u32p]),
     "matrix_vector_multiply_transform_weight_cuda_b200": (C.c_int, [_TDp, _vp, _TDp, _vp, _vp]),

@@ -302,6 +302,8 @@ EE bolt_b200_gemm_u8s8_ex(U32 N, U32 M, U32 K, const void *A, const void *packed
     ep.row_scale = e->row_scale;
     ep.col_scale = e->col_scale;
     ep.col_factor = e->col_factor;
+    ep.prefetch = e->prefetch;
+    ep.prefetch_bytes = e->prefetch_bytes;
     if (e->col_factor != nullptr && e->row_scale != nullptr) {
         return NOT_SUPPORTED;
     }

@@ -371,14 +371,10 @@ EE bnn_run(const TensorDesc *inputDesc, const void *input, const TensorDesc *fil
     if (smem > 200 * 1024) {
         return NOT_SUPPORTED;
     }
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] {
-        cudaError_t e1 = cudaFuncSetAttribute(bnn_conv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        cudaError_t e2 = cudaFuncSetAttribute(bnn_conv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        attr_err = e1 != cudaSuccess ? e1 : e2;
-    });
-    B200_CUDA(attr_err);
+    {
+        const void *ks[2] = {(const void *)bnn_conv_kernel<true>, (const void *)bnn_conv_kernel<false>};
+        B200_EE(raise_smem_limit(c, KF_BNN, ks, 2, 200 * 1024));
+    }
     const size_t npix = (size_t)g.out.n * g.out.h * g.out.w;
     dim3 grid((uint32_t)((npix + PIX_TILE - 1) / PIX_TILE), (g.out.c + OC_TILE - 1) / OC_TILE);
     if (xnor) {

@@ -54,8 +54,15 @@ struct WeightTwin {
     size_t bytes;
 };
 
+// kernel families whose dynamic shared-memory limit has to be raised above 48 KiB; the attribute
+// belongs to the device that is current when it is set, so it is remembered per device context
+enum KernelFamily { KF_GEMM = 0, KF_CONV, KF_GEMV, KF_GEMV_ROW, KF_BNN, KF_COUNT };
+
 struct DeviceCtx {
     int device = 0;
+    bool smem_raised[KF_COUNT] = {false, false, false, false, false};
+    std::mutex attr_mu;
+    int max_pairs = -1;  // co-resident 2-CTA clusters of the tensor-core GEMM (-1: not queried yet)
     int sm_count = 148;
     int *d_status = nullptr;      // device-side error word
     float *d_scratch = nullptr;   // small device scratch for reductions (absmax etc.)
@@ -84,6 +91,10 @@ inline void count_launch(int n = 1)
 {
     g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed);
 }
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize for every kernel of a family, once per device
+// (the calling thread's device must be current, which ctx() guarantees)
+EE raise_smem_limit(DeviceCtx *c, KernelFamily f, const void *const *kernels, int n, size_t bytes);
 
 // true if p is memory the GPU can dereference (device or managed)
 bool is_device_ptr(const void *p);
@@ -140,7 +151,7 @@ EE cuda_ee(cudaError_t e);
 // rank <= 5; zero fill out of range.  `map` points at a CUtensorMap.
 bool tensor_map_encoder_available();
 bool encode_tiled_u8(void *map, uint32_t rank, const void *base, const uint64_t *dims, const uint64_t *strides,
-    const uint32_t *box, const uint32_t *elem_strides, int swizzle_bytes /* 0, 64 or 128 */);
+    const uint32_t *box, const uint32_t *elem_strides, int swizzle_bytes /* 0, 32, 64 or 128 */);
 
 // ---- kernel launchers (device pointers only) ----------------------------------------------
 struct GemmEpilogue {
@@ -154,6 +165,8 @@ struct GemmEpilogue {
     const float *row_scale;    // [M] or null
     const float *col_scale;    // [N] or null
     const float *col_factor;   // [N] or null: ready-made per-column factors (then nothing is divided in the kernel)
+    const void *prefetch;      // device memory a later call will read (the next layer's weight), or null:
+    size_t prefetch_bytes;     // brought into L2 while this GEMM runs
 };
 
 // B: ALIGN(N,16) rows, pitch Kp = ALIGN(K,8) bytes, K contiguous, zero padded.

@@ -69,6 +69,19 @@ DeviceCtx *ctx()
     return g_ctx[dev];
 }
 
+EE raise_smem_limit(DeviceCtx *c, KernelFamily f, const void *const *kernels, int n, size_t bytes)
+{
+    std::lock_guard<std::mutex> g(c->attr_mu);
+    if (c->smem_raised[f]) {
+        return SUCCESS;
+    }
+    for (int i = 0; i < n; ++i) {
+        B200_CUDA(cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    }
+    c->smem_raised[f] = true;
+    return SUCCESS;
+}
+
 bool is_device_ptr(const void *p)
 {
     if (p == nullptr) {

@@ -570,19 +570,11 @@ EE launch_conv_tcgen05(const uint8_t *xp, const int8_t *w, const int32_t *offs, 
     if (c == nullptr) {
         return UNKNOWN;
     }
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] {
+    {
         const void *ks[3] = {(const void *)conv_u8s8_tcgen05_kernel<0>, (const void *)conv_u8s8_tcgen05_kernel<1>,
             (const void *)conv_u8s8_tcgen05_kernel<2>};
-        for (const void *k : ks) {
-            cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
-            if (e != cudaSuccess) {
-                attr_err = e;
-            }
-        }
-    });
-    B200_CUDA(attr_err);
+        B200_EE(raise_smem_limit(c, KF_CONV, ks, 3, SMEM_BYTES));
+    }
     if (!tensor_map_encoder_available()) {
         return NOT_SUPPORTED;
     }

@@ -5,17 +5,25 @@
 // Replaces the AVX512-VNNI micro-kernels and their driver in Bolt
 // (compute/blas_enhance/src/cpu/x86/int8/avx512/mmm_avx512_vnni.cpp:383-1891).
 //
-// One persistent CTA per SM, 320 threads, three roles:
+// One persistent CTA per SM, three roles:
 //   warp 0      TMA producer: cp.async.bulk.tensor 2-D loads of a 128 x 128-byte A tile and a
 //               BLOCK_N x 128-byte B tile per pipeline stage, 128-byte swizzle, mbarrier complete_tx
 //   warp 1      MMA issuer: one thread issues tcgen05.mma.cta_group::1.kind::i8 (M=128, N=BLOCK_N,
 //               K=32 per instruction, A unsigned / B signed, int32 accumulate, no saturation) with
 //               shared-memory matrix descriptors; accumulators live in tensor memory (2 x 256 columns,
 //               so the epilogue of tile i overlaps the main loop of tile i+1)
-//   warps 2..9  epilogue, two warps per scheduler: the pair that shares a tensor-memory lane quadrant
-//               splits the tile's columns; tcgen05.ld of 32 lanes x 32 columns, software pipelined
-//               (the next chunk is in flight while this one is converted), fused offsetC / C_in add and
-//               the reference's s32 -> f32 / u8 conversions, 16-byte global stores
+//   warps 2..   epilogue.  The fast instantiations run 16 epilogue warps, four per scheduler: the four
+//               warps that share a tensor-memory lane quadrant split the tile's columns (at most 64
+//               each), read their whole share with tcgen05.ld, hand the accumulator back to the MMA
+//               warp at once and only then convert: +offsetC, s32 -> f32, * factor as packed f32x2
+//               operations, and for u8 the rounding by a biased add whose low byte is the result
+//               (out-of-range values are detected by one OR per element and redone exactly).  u8 tiles
+//               leave through swizzled staging and TMA stores.  The general instantiation (ragged N,
+//               accumulate into C) keeps 8 epilogue warps and plain stores.
+// Tiles are visited in groups of 16 row blocks x all column blocks, so that the CTAs of one wave
+// share a few A and B panels in L2.  The kernel is launched with programmatic stream serialization:
+// its set-up (barriers, tensor-memory allocation, descriptor prefetch) overlaps the tail of the
+// previous kernel of the stream; nothing is read or written before griddepcontrol.wait.
 // Every mbarrier wait is bounded; a wait that runs out sets the device status word and the CTA
 // drains and exits (tensor memory is always released).
 #include <cuda.h>
@@ -30,12 +38,13 @@ using namespace tc;
 
 constexpr int MAX_BLOCK_N = 256;
 constexpr int MAX_STAGES = 8;        // the ring is as deep as shared memory allows for the tile width
-constexpr int EPI_WARPS = 8;
-constexpr int EPI_THREADS = EPI_WARPS * 32;
-constexpr int NUM_THREADS = 64 + EPI_THREADS;
+constexpr int EPI_WARPS_FAST = 16;
+constexpr int EPI_WARPS_GENERAL = 8;
 constexpr uint32_t TMEM_COLS = 512;  // 2 accumulators x 256 columns
+constexpr uint32_t GROUP_M = 16;     // row blocks per raster group
 
 constexpr int SMEM_A_STAGE = BLOCK_M * BLOCK_K;        // 16 KiB
+constexpr int CONST_SLOTS = 1024;    // per-warp column constants: EPI_WARPS x (256 / column groups)
 
 struct __align__(16) SmemCtl {
     uint64_t full[MAX_STAGES];
@@ -44,16 +53,16 @@ struct __align__(16) SmemCtl {
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
-    // per epilogue warp: offsetC and conversion factor of the (at most 128) columns it owns
-    __align__(16) int32_t offs[EPI_WARPS][128];
-    __align__(16) float colf[EPI_WARPS][128];
+    // per epilogue warp: offsetC and conversion factor of the columns it owns
+    __align__(16) int32_t offs[CONST_SLOTS];
+    __align__(16) float colf[CONST_SLOTS];
 };
 
-// 227 KiB per CTA: alignment slack + control block + as many (A tile, B tile) stages as fit
+// 227 KiB per CTA: alignment slack + control block + staging + as many (A tile, B tile) stages as fit
 constexpr size_t SMEM_BYTES = 232448;
-// u8 tiles leave through TMA stores: each epilogue warp stages 32 rows x 64 bytes (64-byte swizzle)
-constexpr int STAGING_PER_WARP = 32 * 64;
-constexpr size_t SMEM_STAGING_BYTES = (size_t)EPI_WARPS * STAGING_PER_WARP;  // 16 KiB
+// u8 tiles leave through TMA stores: each epilogue warp stages 32 rows x 32 bytes (32-byte swizzle)
+constexpr int STAGING_PER_WARP = 32 * 32;
+constexpr size_t SMEM_STAGING_BYTES = (size_t)EPI_WARPS_FAST * STAGING_PER_WARP;  // 16 KiB
 constexpr size_t SMEM_RING_BYTES = (SMEM_BYTES - 1024 - sizeof(SmemCtl) - SMEM_STAGING_BYTES) & ~(size_t)1023;
 
 struct Params {
@@ -65,55 +74,132 @@ struct Params {
     GemmEpilogue ep;
     int *status;
     int vec_ok;             // rows of C are 16-byte aligned -> vector stores allowed
+    uint32_t prefetch_slice;  // bytes of ep.prefetch each CTA asks for (0: none)
 };
 
-// ---- epilogue for 32 consecutive columns of one row: the common case ---------------------------
-// Full, 16-byte aligned chunk, C overwritten, one conversion factor per column.  Kept free of
-// branches and small, because each epilogue warp runs it 4 to 8 times per tile back to back and
-// the instruction stream has to stay resident.  Per element: add offsetC, s32 -> f32 (vcvtdq2ps),
-// multiply (vmulps), then for u8 the bias-add rounding of f32_to_u8_zp128.
-// 32 accumulators of one row -> 32 bytes (8 words): +offsetC, s32 -> f32, * factor, round, +128, clamp
-__device__ __forceinline__ void chunk_to_u8(const int32_t *offs, const float *colf, uint32_t cl, const uint32_t (&r)[32],
-    uint32_t (&w)[8])
+// Raster: groups of GROUP_M row blocks, inside a group the row block runs fastest.
+__device__ __forceinline__ void tile_coords(const Params &p, uint32_t tile, uint32_t &mb, uint32_t &nb)
 {
+    const uint32_t per_group = GROUP_M * p.tiles_n;
+    const uint32_t g = tile / per_group;
+    const uint32_t first = g * GROUP_M;
+    const uint32_t gm = min(GROUP_M, p.tiles_m - first);
+    const uint32_t r = tile - g * per_group;
+    nb = r / gm;
+    mb = first + (r - nb * gm);
+}
+
+// ---- epilogue for 32 consecutive columns of one row: the common case ---------------------------
+// Full, 16-byte aligned chunk, C overwritten.  Per element: add offsetC, s32 -> f32 (vcvtdq2ps),
+// multiply (vmulps), then for u8 the rounding of vcvtps2dq + vpaddd 128 + vpmovusdb.
+//
+// 32 accumulators of one row -> 32 bytes (8 words), the common case: f + (1.5 * 2^23 + 128) has the bits
+// 0x4B400000 + (rne(f) + 128) whenever -128 <= rne(f) <= 127 (the sum lies in [2^23, 2^24), where one ulp
+// is 1 and ties go to the even sum, i.e. to even rne(f)), so the low byte is the result; every other
+// input -- too large, too negative, NaN, infinity -- leaves other upper bits.  Returns the OR of
+// (bits ^ 0x4B400000) over the chunk: above 255 means that some element needs the exact routine.
+template <bool ROWS>
+__device__ __forceinline__ uint32_t chunk_to_u8_quick(const int32_t *offs, const float *colf, uint32_t cl, float num, float rs,
+    const uint32_t (&r)[32], uint32_t (&w)[8])
+{
+    constexpr uint32_t BIAS_BITS = 0x4B400000u;
+    uint32_t seen = 0;
 #pragma unroll
     for (int j = 0; j < 32; j += 4) {
         const int4 o = *reinterpret_cast<const int4 *>(offs + cl + j);
-        const float4 c4 = *reinterpret_cast<const float4 *>(colf + cl + j);
+        float4 c4 = *reinterpret_cast<const float4 *>(colf + cl + j);
+        if (ROWS) {
+            c4.x = __fdiv_rn(num, __fmul_rn(rs, c4.x));
+            c4.y = __fdiv_rn(num, __fmul_rn(rs, c4.y));
+            c4.z = __fdiv_rn(num, __fmul_rn(rs, c4.z));
+            c4.w = __fdiv_rn(num, __fmul_rn(rs, c4.w));
+        }
+        const uint32_t u0 = __float_as_uint(__fadd_rn(__fmul_rn(__int2float_rn((int)r[j] + o.x), c4.x), 12583040.0f));
+        const uint32_t u1 = __float_as_uint(__fadd_rn(__fmul_rn(__int2float_rn((int)r[j + 1] + o.y), c4.y), 12583040.0f));
+        const uint32_t u2 = __float_as_uint(__fadd_rn(__fmul_rn(__int2float_rn((int)r[j + 2] + o.z), c4.z), 12583040.0f));
+        const uint32_t u3 = __float_as_uint(__fadd_rn(__fmul_rn(__int2float_rn((int)r[j + 3] + o.w), c4.w), 12583040.0f));
+        seen |= (u0 ^ BIAS_BITS);
+        seen |= (u1 ^ BIAS_BITS);
+        seen |= (u2 ^ BIAS_BITS);
+        seen |= (u3 ^ BIAS_BITS);
+        w[j >> 2] = __byte_perm(__byte_perm(u0, u1, 0x0040), __byte_perm(u2, u3, 0x0040), 0x5410);
+    }
+    return seen;
+}
+// The same chunk with the exact conversion (any input).  Rare -- an element beyond the u8 range means
+// that the output scale does not fit the data -- so it is kept out of line and fetches the accumulators
+// again from tensor memory instead of keeping them alive across the common path.  Called by whole warps.
+struct Words8 {
+    uint32_t w[8];
+};
+template <bool ROWS>
+__device__ __noinline__ Words8 chunk_to_u8_exact(uint32_t taddr, const int32_t *offs, const float *colf, uint32_t cl,
+    float num, float rs)
+{
+    uint32_t r[32];
+    tmem_ld32(taddr, r);
+    tmem_ld_wait(r);
+    Words8 out;
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+        const int4 o = *reinterpret_cast<const int4 *>(offs + cl + j);
+        float4 c4 = *reinterpret_cast<const float4 *>(colf + cl + j);
+        if (ROWS) {
+            c4.x = __fdiv_rn(num, __fmul_rn(rs, c4.x));
+            c4.y = __fdiv_rn(num, __fmul_rn(rs, c4.y));
+            c4.z = __fdiv_rn(num, __fmul_rn(rs, c4.z));
+            c4.w = __fdiv_rn(num, __fmul_rn(rs, c4.w));
+        }
         const uint32_t b0 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j] + o.x), c4.x));
         const uint32_t b1 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j + 1] + o.y), c4.y));
         const uint32_t b2 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j + 2] + o.z), c4.z));
         const uint32_t b3 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j + 3] + o.w), c4.w));
-        w[j >> 2] = __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
+        out.w[j >> 2] = __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
+    }
+    return out;
+}
+// quick conversion, redone exactly for the whole warp when any lane saw an element out of range
+template <bool ROWS>
+__device__ __forceinline__ void chunk_to_u8(uint32_t taddr, const int32_t *offs, const float *colf, uint32_t cl, float num,
+    float rs, const uint32_t (&r)[32], uint32_t (&w)[8])
+{
+    const uint32_t seen = chunk_to_u8_quick<ROWS>(offs, colf, cl, num, rs, r, w);
+    if (__any_sync(0xffffffffu, seen > 255u)) {
+        const Words8 e = chunk_to_u8_exact<ROWS>(taddr, offs, colf, cl, num, rs);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            w[q] = e.w[q];
+        }
     }
 }
-// 32 bytes of row `lane` into the warp's staging box [32 rows][64 B], 64-byte swizzle: the 16-byte
-// chunk index is XORed with bits 1..2 of the row, the pattern the TMA store undoes
-__device__ __forceinline__ void stage_u8(uint8_t *stg, uint32_t lane, uint32_t which, const uint32_t (&w)[8])
+// 32 bytes of row `lane` into the warp's staging box [32 rows][32 B], 32-byte swizzle: the 16-byte
+// chunk index is XORed with bit 2 of the row (address bit 7 into bit 4), the pattern the TMA store undoes
+__device__ __forceinline__ void stage_u8(uint8_t *stg, uint32_t lane, const uint32_t (&w)[8])
 {
-    const uint32_t sw = (lane >> 1) & 3;
-    uint8_t *row = stg + lane * 64;
-    *reinterpret_cast<uint4 *>(row + (((which * 2) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-    *reinterpret_cast<uint4 *>(row + (((which * 2 + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+    const uint32_t sw = (lane >> 2) & 1;
+    uint8_t *row = stg + lane * 32;
+    *reinterpret_cast<uint4 *>(row + ((0 ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<uint4 *>(row + ((1 ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
 }
 
-template <int KIND>
-__device__ __forceinline__ void store_chunk_fast(void *C, uint32_t N, const int32_t *offs, const float *colf,
-    uint32_t m, uint32_t n0, uint32_t cl, const uint32_t (&r)[32])
+// KIND 0 s32, 1 f32, 2 u8: direct 16-byte stores of one row's 32 columns
+template <int KIND, bool ROWS>
+__device__ __forceinline__ void store_chunk_fast(void *C, uint32_t N, const int32_t *offs, const float *colf, float num,
+    float rs, uint32_t m, uint32_t n0, uint32_t cl, const uint32_t (&r)[32])
 {
     const size_t row_off = (size_t)m * N + n0;
-    if (KIND == 2) {
-        uint32_t w[8];
-        chunk_to_u8(offs, colf, cl, r, w);
-        uint8_t *out = reinterpret_cast<uint8_t *>(C) + row_off;
-        *reinterpret_cast<uint4 *>(out) = make_uint4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<uint4 *>(out + 16) = make_uint4(w[4], w[5], w[6], w[7]);
-    } else if (KIND == 1) {
+    if (KIND == 1) {
         float *out = reinterpret_cast<float *>(C) + row_off;
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
             const int4 o = *reinterpret_cast<const int4 *>(offs + cl + j);
-            const float4 c4 = *reinterpret_cast<const float4 *>(colf + cl + j);
+            float4 c4 = *reinterpret_cast<const float4 *>(colf + cl + j);
+            if (ROWS) {
+                c4.x = __fdiv_rn(num, __fmul_rn(rs, c4.x));
+                c4.y = __fdiv_rn(num, __fmul_rn(rs, c4.y));
+                c4.z = __fdiv_rn(num, __fmul_rn(rs, c4.z));
+                c4.w = __fdiv_rn(num, __fmul_rn(rs, c4.w));
+            }
             *reinterpret_cast<float4 *>(out + j) = make_float4(acc_to_f32((int)r[j] + o.x, c4.x),
                 acc_to_f32((int)r[j + 1] + o.y, c4.y), acc_to_f32((int)r[j + 2] + o.z, c4.z),
                 acc_to_f32((int)r[j + 3] + o.w, c4.w));
@@ -130,7 +216,7 @@ __device__ __forceinline__ void store_chunk_fast(void *C, uint32_t N, const int3
 }
 
 // ---- epilogue for 32 consecutive columns of one row: every other case ---------------------------
-// (ragged or unaligned N, accumulate into C, per-row scales)
+// (ragged or unaligned N, accumulate into C)
 __device__ __forceinline__ void store_chunk(const Params &p, const int32_t *offs, const float *colf, uint32_t m,
     uint32_t n0 /*global col of r[0]*/, uint32_t cl /*tile-local col of r[0]*/, const uint32_t (&r)[32])
 {
@@ -251,17 +337,31 @@ __device__ __forceinline__ void store_chunk(const Params &p, const int32_t *offs
 }
 
 // KIND >= 0: the fast epilogue for that output kind (0 s32, 1 f32, 2 u8 with direct stores, 3 u8 through
-// swizzled staging + TMA stores described by map_c); KIND < 0: the general one.
-template <int KIND>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+// swizzled staging + TMA stores described by map_c), ROWS: one activation scale per row; KIND < 0: the
+// general epilogue.  EW = number of epilogue warps (a multiple of 4).
+//
+// PAIR: the grid is launched as clusters of two CTAs that share one tcgen05.mma.cta_group::2 of 256 rows:
+// CTA r of the pair loads its own 128 rows of A and half of the B tile's rows, so every SM fetches
+// (128 + BLOCK_N / 2) x 128 bytes per stage instead of (128 + BLOCK_N) x 128 -- the main loop is bound by
+// the operand bytes an SM can take in per clock, and this is a third less of them.  The CTA of cluster
+// rank 0 issues the MMAs for both and signals both through tcgen05.commit to the two CTAs' barriers;
+// every load completes on the leader's barrier; each CTA reads its own 128 accumulator rows.
+template <int KIND, bool ROWS, int EW, bool PAIR>
+__global__ void __launch_bounds__(64 + EW * 32, 1)
 gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
     const __grid_constant__ CUtensorMap map_c, const Params p)
 {
+    constexpr uint32_t GROUPS = EW / 4;                 // column groups per lane quadrant
+    constexpr uint32_t SLOTS = CONST_SLOTS / EW;        // constants per warp: 64 (16 warps) or 128 (8 warps)
     extern __shared__ uint8_t smem_raw[];
     // 128-byte swizzled tiles need 1024-byte aligned bases
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *smem_a = smem;
-    const uint32_t b_stage = p.block_n * BLOCK_K;  // multiple of 4 KiB: every stage stays 1024-byte aligned
+    const uint32_t b_rows = PAIR ? (p.block_n >> 1) : p.block_n;  // rows of the B tile this CTA holds
+    const uint32_t b_stage = (b_rows * BLOCK_K + 1023u) & ~1023u;  // every stage stays 1024-byte aligned
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+    const uint32_t cta = PAIR ? (blockIdx.x >> 1) : blockIdx.x;       // index among the tile workers
+    const uint32_t workers = PAIR ? (gridDim.x >> 1) : gridDim.x;
     uint8_t *smem_b = smem + p.stages * SMEM_A_STAGE;
     uint8_t *smem_staging = smem + SMEM_RING_BYTES;  // 1024-byte aligned
     SmemCtl *ctl = reinterpret_cast<SmemCtl *>(smem + SMEM_RING_BYTES + SMEM_STAGING_BYTES);
@@ -269,51 +369,101 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t num_tiles = p.tiles_m * p.tiles_n;
-    const uint32_t stage_bytes = (uint32_t)(BLOCK_M + p.block_n) * BLOCK_K;
+    // bytes that complete on one full barrier: both CTAs' tiles in pair mode
+    const uint32_t stage_bytes = (PAIR ? 2u : 1u) * (uint32_t)(BLOCK_M + b_rows) * BLOCK_K;
+    const uint32_t nch = p.block_n >> 5;
+    const uint32_t cpg = (nch + GROUPS - 1) / GROUPS;          // 32-column chunks per column group
+    const uint32_t active_groups = (nch + cpg - 1) / cpg;
 
     if (threadIdx.x == 0) {
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+        if (KIND == 3) {
+            prefetch_tensormap(&map_c);
+        }
         for (int s = 0; s < MAX_STAGES; ++s) {
             mbar_init(&ctl->full[s], 1);
             mbar_init(&ctl->empty[s], 1);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&ctl->tmem_full[a], 1);
-            mbar_init(&ctl->tmem_empty[a], EPI_THREADS);
+            // one arrival per working epilogue warp (of both CTAs in pair mode)
+            mbar_init(&ctl->tmem_empty[a], (PAIR ? 8 : 4) * active_groups);
         }
         ctl->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                         smem_u32(&ctl->tmem_base)),
-                     "r"(TMEM_COLS)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) {
+            // the same warp of both CTAs of the pair allocates
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                             smem_u32(&ctl->tmem_base)),
+                         "r"(TMEM_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                             smem_u32(&ctl->tmem_base)),
+                         "r"(TMEM_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
+    // the next kernel of the stream may start its own set-up now; it reads nothing before its wait
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     tcgen05_fence_before();
     __syncthreads();
+    if (PAIR) {
+        cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
+    }
     tcgen05_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
+    // everything the previous kernels of the stream wrote is visible after this
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == 0) {
         // ------------------------------- TMA producer -------------------------------------------
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-                const int m0 = (int)((tile % p.tiles_m) * BLOCK_M);
-                const int n0 = (int)((tile / p.tiles_m) * p.block_n);
+            // this CTA's slice of the memory a later kernel will read, requested once the pipeline is filled
+            uint32_t issued = 0;
+            const uint32_t fill = min(p.stages, p.num_kb);
+            for (uint32_t tile = cta; ok && tile < num_tiles; tile += workers) {
+                uint32_t mb, nb;
+                tile_coords(p, tile, mb, nb);
+                const int m0 = (int)((PAIR ? 2 * mb + rank : mb) * BLOCK_M);
+                const int n0 = (int)(nb * p.block_n + rank * b_rows);
                 for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
                     if (!mbar_wait(&ctl->empty[stage], phase ^ 1)) {
                         ok = false;
                         break;
                     }
-                    mbar_expect_tx(&ctl->full[stage], stage_bytes);
-                    tma_load_2d(&map_a, &ctl->full[stage], smem_a + stage * SMEM_A_STAGE, (int)(kb * BLOCK_K), m0);
-                    tma_load_2d(&map_b, &ctl->full[stage], smem_b + stage * b_stage, (int)(kb * BLOCK_K), n0);
+                    if (PAIR) {
+                        // both CTAs' bytes are expected by, and complete on, the leader's barrier
+                        const uint32_t bar = mapa_shared(smem_u32(&ctl->full[stage]), 0);
+                        if (rank == 0) {
+                            mbar_expect_tx(&ctl->full[stage], stage_bytes);
+                        }
+                        tma_load_2d_pair(&map_a, bar, smem_a + stage * SMEM_A_STAGE, (int)(kb * BLOCK_K), m0);
+                        tma_load_2d_pair(&map_b, bar, smem_b + stage * b_stage, (int)(kb * BLOCK_K), n0);
+                    } else {
+                        mbar_expect_tx(&ctl->full[stage], stage_bytes);
+                        tma_load_2d(&map_a, &ctl->full[stage], smem_a + stage * SMEM_A_STAGE, (int)(kb * BLOCK_K), m0);
+                        tma_load_2d(&map_b, &ctl->full[stage], smem_b + stage * b_stage, (int)(kb * BLOCK_K), n0);
+                    }
                     if (++stage == p.stages) {
                         stage = 0;
                         phase ^= 1;
+                    }
+                    if (++issued == fill && p.prefetch_slice != 0) {
+                        const size_t off = (size_t)blockIdx.x * p.prefetch_slice;
+                        if (off < p.ep.prefetch_bytes) {
+                            const size_t n = min((size_t)p.prefetch_slice, p.ep.prefetch_bytes - off) & ~(size_t)15;
+                            if (n != 0) {
+                                prefetch_l2_bulk(reinterpret_cast<const uint8_t *>(p.ep.prefetch) + off, (uint32_t)n);
+                            }
+                        }
                     }
                 }
             }
@@ -325,12 +475,12 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         __syncwarp();
     } else if (warp == 1) {
         // ------------------------------- MMA issuer ---------------------------------------------
-        if (lane == 0) {
-            const uint32_t idesc = make_idesc_i8(p.block_n);
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = make_idesc_i8(p.block_n, PAIR ? 2 * BLOCK_M : BLOCK_M);
             uint32_t stage = 0, phase = 0;
             uint32_t it = 0;
             bool ok = true;
-            for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++it) {
+            for (uint32_t tile = cta; ok && tile < num_tiles; tile += workers, ++it) {
                 const uint32_t acc = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1;
                 if (!mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1)) {
@@ -351,9 +501,18 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     for (uint32_t k = 0; k < BLOCK_K / UMMA_K; ++k) {
                         // advancing K inside the 128-byte swizzle row: +32 bytes = +2 in the
                         // 16-byte units of the descriptor's start-address field
-                        umma_i8(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        if (PAIR) {
+                            umma_i8_pair(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        } else {
+                            umma_i8(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        }
                     }
-                    tcgen05_commit(&ctl->empty[stage]);  // frees the stage once these MMAs retire
+                    // frees the stage (in both CTAs) once these MMAs retire
+                    if (PAIR) {
+                        tcgen05_commit_pair(&ctl->empty[stage]);
+                    } else {
+                        tcgen05_commit(&ctl->empty[stage]);
+                    }
                     if (++stage == p.stages) {
                         stage = 0;
                         phase ^= 1;
@@ -362,7 +521,11 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 if (!ok) {
                     break;
                 }
-                tcgen05_commit(&ctl->tmem_full[acc]);
+                if (PAIR) {
+                    tcgen05_commit_pair(&ctl->tmem_full[acc]);
+                } else {
+                    tcgen05_commit(&ctl->tmem_full[acc]);
+                }
             }
             if (!ok) {
                 atomicExch(p.status, 2);
@@ -371,27 +534,28 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         }
         __syncwarp();
     } else {
-        // ------------------------------- epilogue warps 2..9 ------------------------------------
-        const uint32_t quad = warp & 3;         // tensor-memory lane quadrant this warp may read
-        const uint32_t half = (warp - 2) >> 2;  // which half of the tile's columns
-        uint8_t *stg = smem_staging + (warp - 2) * STAGING_PER_WARP;
+        // ------------------------------- epilogue warps -----------------------------------------
+        const uint32_t ew = warp - 2;
+        const uint32_t quad = warp & 3;   // tensor-memory lane quadrant this warp may read
+        const uint32_t grp = ew >> 2;     // which share of the tile's columns
+        uint8_t *stg = smem_staging + ew * STAGING_PER_WARP;
         const GemmEpilogue &ep = p.ep;
-        const uint32_t nch = p.block_n >> 5;
-        const uint32_t c_begin = half ? ((nch + 1) >> 1) : 0u;
-        const uint32_t c_end = half ? nch : ((nch + 1) >> 1);
+        const uint32_t c_begin = min(nch, grp * cpg);
+        const uint32_t c_end = min(nch, c_begin + cpg);
         // Column constants (offsetC and the conversion factor): every warp keeps those of its own
-        // columns in its own slice of shared memory, lane l owning columns l, l+32, l+64, l+96 of the
-        // warp's range.  The next tile's values are fetched into registers before the current
-        // accumulator is awaited and written after the tile's chunks, so neither the global-load
-        // latency nor any CTA-wide barrier sits between two tiles; warps drift freely.
-        // The loads are volatile asm so that they stay where they are written (early); everything
-        // that depends on them is written after the tile's chunks (late).
-        int32_t *offs = ctl->offs[warp - 2];
-        float *colf = ctl->colf[warp - 2];
+        // columns in its own slice of shared memory, lane l owning columns l, l+32, ... of the warp's
+        // range.  The next tile's values are fetched into registers before the current accumulator
+        // is awaited and written after the tile's chunks, so neither the global-load latency nor any
+        // CTA-wide barrier sits between two tiles; warps drift freely.  The loads are volatile asm
+        // so that they stay where they are written (early); everything that depends on them is
+        // written after the tile's chunks (late).
+        int32_t *offs = ctl->offs + ew * SLOTS;
+        float *colf = ctl->colf + ew * SLOTS;
+        constexpr int NQ = SLOTS / 32;
         const uint32_t my_cols = (c_end - c_begin) * 32;
-        auto fetch_raw = [&](uint32_t tile_n0, int32_t (&o)[4], float (&sb)[4]) {
+        auto fetch_raw = [&](uint32_t tile_n0, int32_t (&o)[NQ], float (&sb)[NQ]) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
+            for (int q = 0; q < NQ; ++q) {
                 o[q] = 0;
                 sb[q] = ep.sB;
                 const uint32_t j = lane + 32 * q;
@@ -422,124 +586,143 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             // with per-row scales the division is done per element; keep sB here
             return ep.row_scale ? sb : __fdiv_rn(ep.num, __fmul_rn(sa_dev, sb));
         };
-        auto park = [&](const int32_t (&o)[4], const float (&sb)[4]) {
+        auto park = [&](const int32_t (&o)[NQ], const float (&sb)[NQ]) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
+            for (int q = 0; q < NQ; ++q) {
                 offs[lane + 32 * q] = o[q];
                 colf[lane + 32 * q] = factor_of(sb[q]);
             }
             __syncwarp();
         };
-        if (blockIdx.x < num_tiles) {
-            int32_t o[4];
-            float sb[4];
-            fetch_raw((blockIdx.x / p.tiles_m) * p.block_n, o, sb);
-            park(o, sb);
-        }
-        uint32_t it = 0;
-        for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
-            const uint32_t acc = it & 1;
-            const uint32_t acc_phase = (it >> 1) & 1;
-            const uint32_t m0 = (tile % p.tiles_m) * BLOCK_M;
-            const uint32_t n0 = (tile / p.tiles_m) * p.block_n;
-            if (*reinterpret_cast<volatile uint32_t *>(&ctl->abort_flag) != 0) {
-                break;  // some role's bounded wait ran out
+        // where this warp reports an accumulator as read: the leader's barrier
+        const uint32_t empty_bar[2] = {PAIR ? mapa_shared(smem_u32(&ctl->tmem_empty[0]), 0) : smem_u32(&ctl->tmem_empty[0]),
+            PAIR ? mapa_shared(smem_u32(&ctl->tmem_empty[1]), 0) : smem_u32(&ctl->tmem_empty[1])};
+        if (c_begin < c_end) {
+            if (cta < num_tiles) {
+                int32_t o[NQ];
+                float sb[NQ];
+                uint32_t mb, nb;
+                tile_coords(p, cta, mb, nb);
+                fetch_raw(nb * p.block_n, o, sb);
+                park(o, sb);
             }
-            const uint32_t next_tile = tile + gridDim.x;
-            int32_t o_next[4];
-            float sb_next[4];
-            if (next_tile < num_tiles) {
-                fetch_raw((next_tile / p.tiles_m) * p.block_n, o_next, sb_next);
+            uint32_t it = 0;
+            uint32_t mb = 0, nb = 0, mb_next = 0, nb_next = 0;
+            if (cta < num_tiles) {
+                tile_coords(p, cta, mb_next, nb_next);
             }
-            bool ok = mbar_wait(&ctl->tmem_full[acc], acc_phase);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) {
-                if (lane == 0) {
-                    atomicExch(p.status, 3);
-                    atomicExch(&ctl->abort_flag, 1u);
+            for (uint32_t tile = cta; tile < num_tiles; tile += workers, ++it) {
+                const uint32_t acc = it & 1;
+                const uint32_t acc_phase = (it >> 1) & 1;
+                mb = mb_next;
+                nb = nb_next;
+                const uint32_t m0 = (PAIR ? 2 * mb + rank : mb) * BLOCK_M;
+                const uint32_t n0 = nb * p.block_n;
+                if (*reinterpret_cast<volatile uint32_t *>(&ctl->abort_flag) != 0) {
+                    break;  // some role's bounded wait ran out
                 }
-                break;
-            }
-            tcgen05_fence_after();
-            const uint32_t m = m0 + quad * 32 + lane;
-            const uint32_t tbase = tmem_base + ((quad * 32u) << 16) + acc * MAX_BLOCK_N;
-            const bool row_ok = m < p.M;
-            uint32_t ra[32], rb[32];
-            if (c_begin < c_end) {
-                tmem_ld32(tbase + c_begin * 32, ra);
-            }
-            bool released = false;
-            for (uint32_t c = c_begin; c < c_end; c += 2) {
-                tmem_ld_wait(ra);
-                const bool has1 = c + 1 < c_end;
-                if (has1) {
-                    tmem_ld32(tbase + (c + 1) * 32, rb);
+                const uint32_t next_tile = tile + workers;
+                int32_t o_next[NQ];
+                float sb_next[NQ];
+                if (next_tile < num_tiles) {
+                    tile_coords(p, next_tile, mb_next, nb_next);
+                    fetch_raw(nb_next * p.block_n, o_next, sb_next);
+                }
+                const uint32_t m = m0 + quad * 32 + lane;
+                const bool row_ok = m < p.M;
+                float rs = 0.f;
+                if (ROWS && row_ok) {
+                    rs = ep.row_scale[m];
+                }
+                bool ok = mbar_wait(&ctl->tmem_full[acc], acc_phase);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) {
+                    if (lane == 0) {
+                        atomicExch(p.status, 3);
+                        atomicExch(&ctl->abort_flag, 1u);
+                    }
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t tbase = tmem_base + ((quad * 32u) << 16) + acc * MAX_BLOCK_N;
+                if (KIND >= 0) {
+                    // One 32-column chunk at a time (at most two per warp): the other three warps of the
+                    // scheduler cover the tensor-memory read latency, and 32 live accumulators keep the
+                    // warp within its register share.  The accumulator goes back to the MMA warp as soon
+                    // as the last chunk has been converted (the rare exact conversion reads it again).
+                    uint32_t ra[32];
+                    for (uint32_t c = c_begin; c < c_end; ++c) {
+                        const uint32_t cl = (c - c_begin) * 32;
+                        tmem_ld32(tbase + c * 32, ra);
+                        tmem_ld_wait(ra);
+                        uint32_t w[8];
+                        if (KIND >= 2) {
+                            chunk_to_u8<ROWS>(tbase + c * 32, offs, colf, cl, ep.num, rs, ra, w);
+                        }
+                        if (c + 1 == c_end) {
+                            tcgen05_fence_before();
+                            __syncwarp();
+                            if (lane == 0) {
+                                // accumulator fully read: the MMA may reuse it
+                                if (PAIR) {
+                                    mbar_arrive_cluster(empty_bar[acc]);
+                                } else {
+                                    mbar_arrive(&ctl->tmem_empty[acc]);
+                                }
+                            }
+                        }
+                        if (KIND == 3) {
+                            // the previous box must have left the staging buffer
+                            if (lane == 0) {
+                                tma_store_wait_read();
+                            }
+                            __syncwarp();
+                            stage_u8(stg, lane, w);
+                            fence_proxy_async_smem();
+                            __syncwarp();
+                            if (lane == 0) {
+                                // rows beyond M are clipped by the tensor map
+                                tma_store_2d(&map_c, stg, (int)(n0 + c * 32), (int)(m0 + quad * 32));
+                            }
+                        } else if (KIND == 2) {
+                            if (row_ok) {
+                                uint8_t *out = reinterpret_cast<uint8_t *>(p.C) + (size_t)m * p.N + n0 + c * 32;
+                                *reinterpret_cast<uint4 *>(out) = make_uint4(w[0], w[1], w[2], w[3]);
+                                *reinterpret_cast<uint4 *>(out + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+                            }
+                        } else if (row_ok) {
+                            store_chunk_fast<KIND, ROWS>(p.C, p.N, offs, colf, ep.num, rs, m, n0 + c * 32, cl, ra);
+                        }
+                    }
                 } else {
+                    uint32_t ra[32];
+                    for (uint32_t c = c_begin; c < c_end; ++c) {
+                        tmem_ld32(tbase + c * 32, ra);
+                        tmem_ld_wait(ra);
+                        if (row_ok && n0 + c * 32 < p.N) {
+                            store_chunk(p, offs, colf, m, n0 + c * 32, (c - c_begin) * 32, ra);
+                        }
+                    }
                     tcgen05_fence_before();
-                    mbar_arrive(&ctl->tmem_empty[acc]);  // accumulator fully read: the MMA may reuse it
-                    released = true;
-                }
-                if (KIND == 3) {
-                    if (has1) {
-                        // first half of a 64-column box: the previous box must have left the staging buffer
-                        if (lane == 0) {
-                            tma_store_wait_read();
-                        }
-                        __syncwarp();
-                        uint32_t w[8];
-                        chunk_to_u8(offs, colf, (c - c_begin) * 32, ra, w);
-                        stage_u8(stg, lane, 0, w);
-                    } else if (row_ok && n0 + c * 32 < p.N) {
-                        store_chunk_fast<2>(p.C, p.N, offs, colf, m, n0 + c * 32, (c - c_begin) * 32, ra);  // odd chunk out
-                    }
-                } else if (row_ok && n0 + c * 32 < p.N) {
-                    if (KIND >= 0) {
-                        store_chunk_fast<KIND>(p.C, p.N, offs, colf, m, n0 + c * 32, (c - c_begin) * 32, ra);
-                    } else {
-                        store_chunk(p, offs, colf, m, n0 + c * 32, (c - c_begin) * 32, ra);
-                    }
-                }
-                if (has1) {
-                    tmem_ld_wait(rb);
-                    if (c + 2 < c_end) {
-                        tmem_ld32(tbase + (c + 2) * 32, ra);
-                    } else {
-                        tcgen05_fence_before();
-                        mbar_arrive(&ctl->tmem_empty[acc]);
-                        released = true;
-                    }
-                    if (KIND == 3) {
-                        uint32_t w[8];
-                        chunk_to_u8(offs, colf, (c + 1 - c_begin) * 32, rb, w);
-                        stage_u8(stg, lane, 1, w);
-                        fence_proxy_async_smem();
-                        __syncwarp();
-                        if (lane == 0 && n0 + c * 32 < p.N) {
-                            // rows beyond M and columns beyond N are clipped by the tensor map
-                            tma_store_2d(&map_c, stg, (int)(n0 + c * 32), (int)(m0 + quad * 32));
-                        }
-                    } else if (row_ok && n0 + (c + 1) * 32 < p.N) {
-                        if (KIND >= 0) {
-                            store_chunk_fast<KIND>(p.C, p.N, offs, colf, m, n0 + (c + 1) * 32, (c + 1 - c_begin) * 32, rb);
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (PAIR) {
+                            mbar_arrive_cluster(empty_bar[acc]);
                         } else {
-                            store_chunk(p, offs, colf, m, n0 + (c + 1) * 32, (c + 1 - c_begin) * 32, rb);
+                            mbar_arrive(&ctl->tmem_empty[acc]);
                         }
                     }
                 }
+                if (next_tile < num_tiles) {
+                    __syncwarp();  // every lane is done reading this tile's constants
+                    park(o_next, sb_next);
+                }
             }
-            if (!released) {
-                tcgen05_fence_before();
-                mbar_arrive(&ctl->tmem_empty[acc]);
+            if (KIND == 3 && lane == 0) {
+                tma_store_wait_all();  // shared memory and the output must be settled before the CTA leaves
             }
-            if (next_tile < num_tiles) {
-                __syncwarp();  // every lane is done reading this tile's constants
-                park(o_next, sb_next);
-            }
+            __syncwarp();
         }
-        if (KIND == 3 && lane == 0) {
-            tma_store_wait_all();  // shared memory and the output must be settled before the CTA leaves
-        }
-        __syncwarp();
     }
 
     __syncthreads();
@@ -550,10 +733,21 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         }
         __syncthreads();
     }
+    if (PAIR) {
+        // neither CTA may leave (or free tensor memory) while its peer can still read its shared
+        // memory through the MMA or arrive on its barriers
+        tcgen05_fence_before();
+        cluster_sync_all();
+    }
     if (warp == 1) {
         tcgen05_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
-                     : "memory");
+        if (PAIR) {
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
+                         : "memory");
+        } else {
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
+                         : "memory");
+        }
     }
 }
 
@@ -590,9 +784,8 @@ bool make_map(CUtensorMap *map, const void *base, uint64_t inner, uint64_t rows,
 
 // Tile width: the widest of 256 / 192 / 128 / 64 / 32 columns that still gives every SM a tile,
 // preferring the one that wastes the least of the last wave.
-uint32_t pick_block_n(uint32_t M, uint32_t N, int sms)
+uint32_t pick_block_n(uint32_t tiles_m, uint32_t N, int sms)
 {
-    const uint32_t tiles_m = (M + BLOCK_M - 1) / BLOCK_M;
     const uint32_t cand[] = {256, 224, 192, 160, 128, 96, 64, 32};
     uint32_t best = 32;
     double best_cost = 1e30;
@@ -638,7 +831,8 @@ bool encode_tiled_u8(void *map, uint32_t rank, const void *base, const uint64_t 
     }
     CUresult r = fn(reinterpret_cast<CUtensorMap *>(map), CU_TENSOR_MAP_DATA_TYPE_UINT8, rank, const_cast<void *>(base), d,
         st, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
-            : (swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
+            : (swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                  : (swizzle_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE)),
         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
@@ -659,6 +853,104 @@ bool gemm_tcgen05_eligible(uint32_t M, uint32_t N, uint32_t K, const void *A, co
     return encode_fn() != nullptr;
 }
 
+namespace {
+
+// One launch, with programmatic stream serialization unless BOLT_B200_NO_PDL is set in the environment
+// (or the runtime refuses the attribute, in which case the plain launch is used from then on).
+// PAIR launches clusters of two CTAs.
+std::atomic<int> g_pdl{-1};
+
+template <int KIND, bool ROWS, int EW, bool PAIR>
+cudaError_t launch_one(uint32_t grid, cudaStream_t st, const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc,
+    const Params &p)
+{
+    int pdl = g_pdl.load(std::memory_order_relaxed);
+    if (pdl < 0) {
+        const char *e = getenv("BOLT_B200_NO_PDL");
+        pdl = (e != nullptr && e[0] != '\0' && e[0] != '0') ? 0 : 1;
+        g_pdl.store(pdl, std::memory_order_relaxed);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(64 + EW * 32);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute at[2];
+    int n = 0;
+    if (PAIR) {
+        at[n].id = cudaLaunchAttributeClusterDimension;
+        at[n].val.clusterDim.x = 2;
+        at[n].val.clusterDim.y = 1;
+        at[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    const int base = n;
+    if (pdl) {
+        at[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    cfg.attrs = at;
+    cfg.numAttrs = n;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_u8s8_tcgen05_kernel<KIND, ROWS, EW, PAIR>, ma, mb, mc, p);
+    if (e != cudaSuccess && pdl) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        cudaStreamIsCapturing(st, &cap);
+        if (cap == cudaStreamCaptureStatusNone) {
+            cudaGetLastError();
+            g_pdl.store(0, std::memory_order_relaxed);
+            cfg.numAttrs = base;
+            e = cudaLaunchKernelEx(&cfg, gemm_u8s8_tcgen05_kernel<KIND, ROWS, EW, PAIR>, ma, mb, mc, p);
+        }
+    }
+    return e;
+}
+
+template <bool PAIR>
+cudaError_t launch_kind(int kind, bool rows, uint32_t grid, cudaStream_t st, const CUtensorMap &ma, const CUtensorMap &mb,
+    const CUtensorMap &mc, const Params &p)
+{
+    constexpr int F = EPI_WARPS_FAST;
+    switch (kind) {
+        case 0:
+            return launch_one<0, false, F, PAIR>(grid, st, ma, mb, mc, p);
+        case 1:
+            return rows ? launch_one<1, true, F, PAIR>(grid, st, ma, mb, mc, p) : launch_one<1, false, F, PAIR>(grid, st, ma, mb, mc, p);
+        case 2:
+            return rows ? launch_one<2, true, F, PAIR>(grid, st, ma, mb, mc, p) : launch_one<2, false, F, PAIR>(grid, st, ma, mb, mc, p);
+        default:
+            return rows ? launch_one<3, true, F, PAIR>(grid, st, ma, mb, mc, p) : launch_one<3, false, F, PAIR>(grid, st, ma, mb, mc, p);
+    }
+}
+
+// How many CTA pairs of the tensor-core kernel the device runs at once (each CTA fills an SM).
+int max_resident_pairs(DeviceCtx *c)
+{
+    std::lock_guard<std::mutex> g(c->attr_mu);
+    if (c->max_pairs < 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * (unsigned)c->sm_count);
+        cfg.blockDim = dim3(64 + EPI_WARPS_FAST * 32);
+        cfg.dynamicSmemBytes = SMEM_BYTES;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2;
+        at[0].val.clusterDim.y = 1;
+        at[0].val.clusterDim.z = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_u8s8_tcgen05_kernel<3, false, EPI_WARPS_FAST, true>, &cfg) != cudaSuccess) {
+            cudaGetLastError();
+            n = 0;
+        }
+        c->max_pairs = n;
+    }
+    return c->max_pairs;
+}
+
+}  // namespace
+
 EE launch_gemm_tcgen05(uint32_t M, uint32_t N, uint32_t K, const uint8_t *A, const int8_t *B, uint32_t Kp,
     void *C, const GemmEpilogue &ep, cudaStream_t st)
 {
@@ -666,73 +958,87 @@ EE launch_gemm_tcgen05(uint32_t M, uint32_t N, uint32_t K, const uint8_t *A, con
     if (c == nullptr) {
         return UNKNOWN;
     }
-    static std::once_flag attr_once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(attr_once, [] {
-        const void *kernels[5] = {(const void *)gemm_u8s8_tcgen05_kernel<-1>, (const void *)gemm_u8s8_tcgen05_kernel<0>,
-            (const void *)gemm_u8s8_tcgen05_kernel<1>, (const void *)gemm_u8s8_tcgen05_kernel<2>,
-            (const void *)gemm_u8s8_tcgen05_kernel<3>};
-        for (const void *k : kernels) {
-            cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
-            if (e != cudaSuccess) {
-                attr_err = e;
-            }
-        }
-    });
-    B200_CUDA(attr_err);
+    {
+        constexpr int F = EPI_WARPS_FAST, G = EPI_WARPS_GENERAL;
+        const void *kernels[] = {(const void *)gemm_u8s8_tcgen05_kernel<-1, false, G, false>,
+            (const void *)gemm_u8s8_tcgen05_kernel<0, false, F, false>, (const void *)gemm_u8s8_tcgen05_kernel<1, false, F, false>,
+            (const void *)gemm_u8s8_tcgen05_kernel<2, false, F, false>, (const void *)gemm_u8s8_tcgen05_kernel<3, false, F, false>,
+            (const void *)gemm_u8s8_tcgen05_kernel<1, true, F, false>, (const void *)gemm_u8s8_tcgen05_kernel<2, true, F, false>,
+            (const void *)gemm_u8s8_tcgen05_kernel<3, true, F, false>,
+            (const void *)gemm_u8s8_tcgen05_kernel<0, false, F, true>, (const void *)gemm_u8s8_tcgen05_kernel<1, false, F, true>,
+            (const void *)gemm_u8s8_tcgen05_kernel<2, false, F, true>, (const void *)gemm_u8s8_tcgen05_kernel<3, false, F, true>,
+            (const void *)gemm_u8s8_tcgen05_kernel<1, true, F, true>, (const void *)gemm_u8s8_tcgen05_kernel<2, true, F, true>,
+            (const void *)gemm_u8s8_tcgen05_kernel<3, true, F, true>};
+        B200_EE(raise_smem_limit(c, KF_GEMM, kernels, (int)(sizeof(kernels) / sizeof(kernels[0])), SMEM_BYTES));
+    }
 
     Params p;
     p.M = M;
     p.N = N;
     p.K = K;
-    p.block_n = pick_block_n(M, N, c->sm_count);
-    p.stages = (uint32_t)(SMEM_RING_BYTES / (SMEM_A_STAGE + (size_t)p.block_n * BLOCK_K));
-    if (p.stages > (uint32_t)MAX_STAGES) {
-        p.stages = MAX_STAGES;
-    }
-    p.tiles_m = (M + BLOCK_M - 1) / BLOCK_M;
-    p.tiles_n = (N + p.block_n - 1) / p.block_n;
-    p.num_kb = (K + BLOCK_K - 1) / BLOCK_K;
     p.C = C;
     p.ep = ep;
     p.status = c->d_status;
     const size_t esz = ep.out_kind == 2 ? 1 : 4;
     p.vec_ok = ((N * esz) % 16 == 0) && (reinterpret_cast<uintptr_t>(C) % 16 == 0);
+    // the fast epilogue needs whole, 16-byte aligned 32-column chunks and no read of C
+    const bool rows = ep.per_channel && ep.row_scale != nullptr;
+    const bool fast = p.vec_ok && (N % 32 == 0) && !(ep.out_kind != 2 && ep.accumulate) && !(rows && ep.out_kind == 0);
+    // CTA pairs: at least two 128-row blocks, a long K (the pair's cluster set-up and its joint first
+    // load cost about a microsecond, which only a main loop of many stages pays back), and a device
+    // that can co-schedule pairs
+    static const bool no_pair = [] {
+        const char *e = getenv("BOLT_B200_NO_PAIR");
+        return e != nullptr && e[0] != '\0' && e[0] != '0';
+    }();
+    const int pairs = (fast && M >= 256 && K >= 4096 && !no_pair) ? max_resident_pairs(c) : 0;
+    const bool pair = pairs > 0;
+    const uint32_t block_m = pair ? 2 * BLOCK_M : BLOCK_M;
+    p.tiles_m = (M + block_m - 1) / block_m;
+    p.block_n = pick_block_n(p.tiles_m, N, pair ? pairs : c->sm_count);
+    const uint32_t b_rows = pair ? p.block_n / 2 : p.block_n;
+    p.stages = (uint32_t)(SMEM_RING_BYTES / (SMEM_A_STAGE + B200_ALIGN((size_t)b_rows * BLOCK_K, 1024)));
+    if (p.stages > (uint32_t)MAX_STAGES) {
+        p.stages = MAX_STAGES;
+    }
+    p.tiles_n = (N + p.block_n - 1) / p.block_n;
+    p.num_kb = (K + BLOCK_K - 1) / BLOCK_K;
 
     CUtensorMap map_a, map_b;
     if (!make_map(&map_a, A, K, M, K, BLOCK_M) ||
-        !make_map(&map_b, B, K, B200_ALIGN(N, 16), Kp, p.block_n)) {
+        !make_map(&map_b, B, K, B200_ALIGN(N, 16), Kp, b_rows)) {
         return NOT_SUPPORTED;
     }
     const uint32_t tiles = p.tiles_m * p.tiles_n;
-    const uint32_t grid = tiles < (uint32_t)c->sm_count ? tiles : (uint32_t)c->sm_count;
-    // the fast epilogue needs whole, 16-byte aligned 32-column chunks, no read of C and one
-    // conversion factor per column
-    const bool fast = p.vec_ok && (N % 32 == 0) && !(ep.out_kind != 2 && ep.accumulate) &&
-        !(ep.per_channel && ep.row_scale != nullptr);
-    // u8 output: 32-row x 64-byte boxes, 64-byte swizzle, stored by TMA from the epilogue's staging
+    const uint32_t workers = pair ? (uint32_t)pairs : (uint32_t)c->sm_count;
+    const uint32_t grid = (tiles < workers ? tiles : workers) * (pair ? 2u : 1u);
+    // u8 output: 32-row x 32-byte boxes, 32-byte swizzle, stored by TMA from the epilogue's staging
     CUtensorMap map_c = map_a;  // placeholder for the kinds that never touch it
     bool tma_c = false;
     if (fast && ep.out_kind == 2) {
         const uint64_t dims[2] = {N, M};
         const uint64_t strides[1] = {N};
-        const uint32_t box[2] = {64, 32};
+        const uint32_t box[2] = {32, 32};
         const uint32_t estr[2] = {1, 1};
-        tma_c = encode_tiled_u8(&map_c, 2, C, dims, strides, box, estr, 64);
+        tma_c = encode_tiled_u8(&map_c, 2, C, dims, strides, box, estr, 32);
     }
+    p.prefetch_slice = 0;
+    if (ep.prefetch != nullptr && ep.prefetch_bytes >= 16 && (reinterpret_cast<uintptr_t>(ep.prefetch) % 16) == 0) {
+        // at most 64 MiB (half of L2), split evenly over the CTAs in 16-byte units
+        const size_t bytes = ep.prefetch_bytes < ((size_t)64 << 20) ? ep.prefetch_bytes : ((size_t)64 << 20);
+        p.ep.prefetch_bytes = bytes;
+        p.prefetch_slice = (uint32_t)B200_ALIGN((bytes + grid - 1) / grid, 16);
+    }
+    cudaError_t e;
     if (!fast) {
-        gemm_u8s8_tcgen05_kernel<-1><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, map_c, p);
-    } else if (ep.out_kind == 0) {
-        gemm_u8s8_tcgen05_kernel<0><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, map_c, p);
-    } else if (ep.out_kind == 1) {
-        gemm_u8s8_tcgen05_kernel<1><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, map_c, p);
-    } else if (tma_c) {
-        gemm_u8s8_tcgen05_kernel<3><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, map_c, p);
+        e = launch_one<-1, false, EPI_WARPS_GENERAL, false>(grid, st, map_a, map_b, map_c, p);
     } else {
-        gemm_u8s8_tcgen05_kernel<2><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, map_c, p);
+        const int kind = ep.out_kind == 2 ? (tma_c ? 3 : 2) : ep.out_kind;
+        e = pair ? launch_kind<true>(kind, rows, grid, st, map_a, map_b, map_c, p)
+                 : launch_kind<false>(kind, rows, grid, st, map_a, map_b, map_c, p);
     }
     count_launch();
-    B200_CUDA(cudaGetLastError());
+    B200_CUDA(e);
     return SUCCESS;
 }
 

@@ -233,12 +233,10 @@ EE launch_gemv_row(uint32_t N, uint32_t K, const uint8_t *Mx, bool transposed, c
     if (smem > 200 * 1024) {
         return NOT_SUPPORTED;
     }
-    static std::once_flag once;
-    static cudaError_t err = cudaSuccess;
-    std::call_once(once, [] {
-        err = cudaFuncSetAttribute(gemv_row_u8s8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    });
-    B200_CUDA(err);
+    {
+        const void *ks[1] = {(const void *)gemv_row_u8s8_kernel};
+        B200_EE(raise_smem_limit(c, KF_GEMV_ROW, ks, 1, 200 * 1024));
+    }
     uint32_t blocks = transposed ? (N + WARPS * 32 - 1) / (WARPS * 32) : (N + WARPS - 1) / WARPS;
     const uint32_t cap = (uint32_t)c->sm_count * 4;
     if (blocks > cap) {
@@ -264,12 +262,10 @@ EE launch_gemv(uint32_t N, uint32_t K, const int8_t *W, uint32_t Kp, const uint8
     if (smem > 200 * 1024) {
         return NOT_SUPPORTED;
     }
-    static std::once_flag once;
-    static cudaError_t err = cudaSuccess;
-    std::call_once(once, [] {
-        err = cudaFuncSetAttribute(gemv_s8u8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    });
-    B200_CUDA(err);
+    {
+        const void *ks[1] = {(const void *)gemv_s8u8_kernel};
+        B200_EE(raise_smem_limit(c, KF_GEMV, ks, 1, 200 * 1024));
+    }
     const int vec_ok = (Kp % 16 == 0) && (reinterpret_cast<uintptr_t>(W) % 16 == 0);
     uint32_t blocks = (N + WARPS - 1) / WARPS;
     // persistent-style grid: every CTA stages x once and then streams many rows (a short-lived CTA

@@ -309,6 +309,19 @@ EE absmax_i32_host(const int32_t *d_x, uint64_t n, int *mx)
     return SUCCESS;
 }
 
+// factor[n] = num / (sA * sB[n]): fp32 multiply, fp32 divide -- the order in which Bolt forms the
+// factor of a layer (fully_connected.cpp:396,409; mmm_avx512_vnni.cpp:1805)
+__global__ void col_factor_kernel(float num, float sA, const float *d_sA, float sB, const float *col_scale, uint32_t N,
+    float *out)
+{
+    const uint32_t n = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n < N) {
+        const float sa = d_sA ? *d_sA : sA;
+        const float sb = col_scale ? col_scale[n] : sB;
+        out[n] = __fdiv_rn(num, __fmul_rn(sa, sb));
+    }
+}
+
 }  // namespace
 
 // int32 (device) -> u8 (device) with the reference's scale protocol; used by the convolution's
@@ -433,6 +446,23 @@ EE bolt_b200_absmax_scale_f32(const F32 *data, uint64_t n, F32 *d_scale)
         count_launch();
     }
     finalize_scale_kernel<<<1, 1, 0, st>>>(bits, d_scale);
+    count_launch();
+    B200_CUDA(cudaGetLastError());
+    return SUCCESS;
+}
+
+EE bolt_b200_col_factor(F32 num, F32 sA, const F32 *d_sA, F32 sB, const F32 *col_scale, U32 N, F32 *factor)
+{
+    if (ctx() == nullptr) {
+        return UNKNOWN;
+    }
+    if (factor == nullptr) {
+        return NULL_POINTER;
+    }
+    if (N == 0) {
+        return SUCCESS;
+    }
+    col_factor_kernel<<<(N + 255) / 256, 256, 0, tls().stream>>>(num, sA, d_sA, sB, col_scale, N, factor);
     count_launch();
     B200_CUDA(cudaGetLastError());
     return SUCCESS;

@@ -12,6 +12,10 @@ constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 128;         // bytes of K per stage
 constexpr int UMMA_K = 32;           // K per tcgen05.mma.kind::i8
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // per wait, about 2 s; far above any legitimate wait
+// A waiting thread is suspended by the hardware until the barrier flips or this many nanoseconds pass;
+// it then polls again.  Long enough that idle warps issue next to nothing, and harmless to latency
+// (the wake-up on completion is immediate).
+constexpr uint32_t TRY_WAIT_SUSPEND_NS = 20000;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
 {
@@ -35,12 +39,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(TRY_WAIT_SUSPEND_NS)
         : "memory");
     return ok != 0;
+}
+// ask for `bytes` (a multiple of 16, at a 16-byte aligned address) to be brought into L2
+__device__ __forceinline__ void prefetch_l2_bulk(const void *p, uint32_t bytes)
+{
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
 // Bounded wait: false when the limit ran out (the caller then aborts the CTA's work).  The bound is
 // counted in SM clock cycles (clock64 is a plain register read; the global nanosecond timer costs
@@ -70,6 +79,10 @@ __device__ __forceinline__ void tma_load_2d(const CUtensorMap *map, uint64_t *ba
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
         : "memory");
 }
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map)
+{
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
 __device__ __forceinline__ void tcgen05_fence_before()
 {
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -93,6 +106,58 @@ __device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t desc_a, uint64
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster share one MMA ---------------------------------
+// The MMA is issued by the CTA of cluster rank 0 and reads A and B from the shared memory of both CTAs
+// (same offsets in each); every CTA keeps its own 128 accumulator rows in its own tensor memory.
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the same shared-memory offset in the CTA of cluster rank `rank`
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// load into this CTA's shared memory, completion bytes counted on the barrier at `bar_cluster_addr`
+// (the leader CTA's barrier); every CTA fetches its own tiles
+__device__ __forceinline__ void tma_load_2d_pair(const CUtensorMap *map, uint32_t bar_cluster_addr, void *dst, int x, int y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void umma_i8_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+    uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrives (once the MMAs issued so far have completed) on the barrier at this offset in both CTAs of the pair
+__device__ __forceinline__ void tcgen05_commit_pair(uint64_t *bar)
+{
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(mask)
+                 : "memory");
+}
+
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
 {
     asm volatile(
@@ -144,9 +209,9 @@ __device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr)
 }
 // Instruction descriptor of kind::i8: D = s32 (2 << 4), A = u8 (0 << 7), B = s8 (1 << 10), both
 // K-major, N >> 3 at bit 17, M >> 4 at bit 24; dense, no saturation.
-__device__ __forceinline__ uint32_t make_idesc_i8(uint32_t n)
+__device__ __forceinline__ uint32_t make_idesc_i8(uint32_t n, uint32_t m = BLOCK_M)
 {
-    return (2u << 4) | (0u << 7) | (1u << 10) | ((n >> 3) << 17) | ((uint32_t)(BLOCK_M >> 4) << 24);
+    return (2u << 4) | (0u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
 

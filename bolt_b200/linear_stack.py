@@ -9,7 +9,7 @@ import ctypes as C
 
 import numpy as np
 
-from . import (CHECK_STATUS, DF_NORMAL, DF_TRANSPOSE, DT_F32, DT_I8, DT_I32, DT_U8_Q, GemmEpilogue, StackLayer, lib,
+from . import (CHECK_STATUS, DF_NORMAL, DF_TRANSPOSE, DT_F32, DT_I8, DT_I32, DT_U8_Q, GemmEpilogue, lib,
                matrix_matrix_multiply_transform_rhs, matrix_matrix_multiply_transform_rhs_bytes, tensor2df)
 
 
@@ -72,8 +72,10 @@ class LinearStack:
         self.launches_per_step = 3 + len(layers)
 
     # ---- pieces -------------------------------------------------------------------------
-    def _gemm(self, l, a_ptr, c_ptr, out_dt, out_scale, sA, d_sA=None, factor=None):
+    def _gemm(self, l, a_ptr, c_ptr, out_dt, out_scale, sA, d_sA=None, factor=None, warm=None):
         ep = GemmEpilogue()
+        # the next layer's packed weight is asked into L2 while this layer computes
+        ep.prefetch, ep.prefetch_bytes = (None, 0) if warm is None else (C.c_void_p(warm.packed.data_ptr()), warm.rhs_bytes)
         ep.col_factor = None if factor is None else C.c_void_p(factor.data_ptr())
         ep.out_dt, ep.accumulate, ep.out_scale = out_dt, 0, float(out_scale)
         ep.sA, ep.sB = float(sA), float(l.w_scale_host[0])
@@ -101,7 +103,8 @@ class LinearStack:
             if i == last:
                 self._gemm(l, self.act[cur].data_ptr(), self.out_dev.data_ptr(), DT_F32, 1.0, sA, d_sA, f)
             else:
-                self._gemm(l, self.act[cur].data_ptr(), self.act[1 - cur].data_ptr(), DT_U8_Q, self.out_scales[i], sA, d_sA, f)
+                self._gemm(l, self.act[cur].data_ptr(), self.act[1 - cur].data_ptr(), DT_U8_Q, self.out_scales[i], sA, d_sA, f,
+                           warm=self.layers[i + 1])
                 sA, d_sA = self.out_scales[i], None
                 cur = 1 - cur
 
@@ -150,63 +153,11 @@ class LinearStack:
                 sA = self.out_scales[i]
         torch.cuda.synchronize()
 
-    # ---- the whole stack as one persistent kernel ----------------------------------------------
-    def build_fused(self):
-        """Plan for bolt_b200_linear_stack_run (needs calibrate() first): per-channel conversion factors
-        of every layer -- layer 0's is recomputed each step from the dynamic input scale -- and the
-        tensor maps, encoded once."""
-        torch = _torch()
-        L = lib()
-        n = len(self.layers)
-        self.factors = [torch.zeros(l.N, dtype=torch.float32, device="cuda") for l in self.layers]
-        descs = (StackLayer * n)()
-        cur, sA = 0, None
-        for i, l in enumerate(self.layers):
-            last = i == n - 1
-            num = 1.0 if last else self.out_scales[i]
-            if i > 0:
-                cs = None if l.uniform else C.c_void_p(l.w_scale.data_ptr())
-                CHECK_STATUS(L.bolt_b200_col_factor(num, sA, None, float(l.w_scale_host[0]), cs, l.N,
-                                                    C.c_void_p(self.factors[i].data_ptr())), "col_factor")
-            descs[i].N, descs[i].K = l.N, l.K
-            descs[i].packedB = l.packed.data_ptr()
-            descs[i].offsetC = l.offsetC_ptr
-            descs[i].col_factor = self.factors[i].data_ptr()
-            descs[i].C = self.out_dev.data_ptr() if last else self.act[1 - cur].data_ptr()
-            descs[i].out_dt = DT_F32 if last else DT_U8_Q
-            if not last:
-                sA, cur = self.out_scales[i], 1 - cur
-        plan = C.c_void_p()
-        CHECK_STATUS(L.bolt_b200_linear_stack_plan(self.M, C.c_void_p(self.act[0].data_ptr()), descs, n, C.byref(plan)),
-                     "linear_stack_plan")
-        torch.cuda.synchronize()
-        self.plan = plan
-        self.launches_per_step_fused = 5  # absmax, scale, quantize, layer-0 factors, the stack kernel
-
-    def step_fused(self):
-        """One pass, device resident, every layer inside one kernel."""
-        L = lib()
-        l0 = self.layers[0]
-        self.quantize_input()
-        num0 = 1.0 if len(self.layers) == 1 else self.out_scales[0]
-        cs = None if l0.uniform else C.c_void_p(l0.w_scale.data_ptr())
-        CHECK_STATUS(L.bolt_b200_col_factor(num0, 1.0, C.c_void_p(self.d_scale.data_ptr()), float(l0.w_scale_host[0]), cs,
-                                            l0.N, C.c_void_p(self.factors[0].data_ptr())), "col_factor")
-        CHECK_STATUS(L.bolt_b200_linear_stack_run(self.plan), "linear_stack_run")
-
-    def free_fused(self):
-        if getattr(self, "plan", None):
-            lib().bolt_b200_linear_stack_free(self.plan)
-            self.plan = None
-
-    def run_host(self, x_host, out_host, fused=False):
+    def run_host(self, x_host, out_host):
         """End to end from pinned host memory: H2D of the fp32 input, one pass, D2H of the fp32 output."""
         torch = _torch()
         self.x_dev.copy_(x_host, non_blocking=True)
-        if fused:
-            self.step_fused()
-        else:
-            self.step()
+        self.step()
         out_host.copy_(self.out_dev, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 

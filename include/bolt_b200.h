@@ -251,32 +251,14 @@ typedef struct {
     const F32 *col_scale; /* device [N], overrides sB */
     const F32 *col_factor; /* device [N]: ready-made conversion factors (bolt_b200_col_factor); when set,
                               out_scale, sA, sB, d_sA and col_scale are not used (row_scale must be NULL) */
+    const void *prefetch;  /* device memory that a later call on this stream will read -- typically the next
+                              layer's packed weight -- or NULL.  The kernel asks for it to be brought into L2
+                              while it computes, so that the next GEMM does not start on cold DRAM reads.  Only a
+                              hint: nothing is written, results do not depend on it. */
+    size_t prefetch_bytes; /* bytes at `prefetch` (tensor-core path only; ignored elsewhere) */
 } bolt_b200_gemm_epilogue;
 EE bolt_b200_gemm_u8s8_ex(U32 N, U32 M, U32 K, const void *A, const void *packedB,
     const I32 *offsetC, void *C, const bolt_b200_gemm_epilogue *ep);
-/* Extension without a counterpart in Bolt (which runs a network one operator at a time,
- * inference/engine/src/cnn.cpp:611-675): a whole stack of quantized linear layers as one persistent,
- * cooperatively launched kernel.  Layer l multiplies the u8 output of layer l-1 (layer 0: A0, u8
- * [M, K_0]) by its packed weight; inner layers store u8, the last one u8 or fp32.  Per layer the
- * arithmetic is that of bolt_b200_gemm_u8s8_ex with one conversion factor per output channel:
- *   DT_U8_Q: C = usat8( rne((float)(acc + offsetC[n]) * col_factor[n]) + 128 )
- *   DT_F32 : C = (float)(acc + offsetC[n]) * col_factor[n]
- * so the result is bit-identical to running the layers one by one.  Tiles of a layer start as soon as
- * the 128-row block they read has been completed by the previous layer (no grid-wide barrier).
- * All pointers are device pointers; N % 32 == 0, K % 16 == 0, K_l == N_{l-1}, at most 32 layers.
- * plan() encodes the tensor maps once (it allocates); run() only enqueues a memset and the kernel on
- * the thread's stream and can be called any number of times; free() releases the plan. */
-typedef struct {
-    U32 N, K;
-    const void *packedB;   /* from matrix_matrix_multiply_transform_rhs_cuda_b200 */
-    const I32 *offsetC;    /* [N], e.g. packedB + rhsBytes, or the bias-folded offset */
-    const F32 *col_factor; /* [N], e.g. from bolt_b200_col_factor */
-    void *C;               /* [M, N] u8 or fp32 */
-    DataType out_dt;       /* DT_U8_Q, or DT_F32 for the last layer */
-} bolt_b200_stack_layer;
-EE bolt_b200_linear_stack_plan(U32 M, const void *A0, const bolt_b200_stack_layer *layers, U32 n_layers, void **plan);
-EE bolt_b200_linear_stack_run(void *plan);
-EE bolt_b200_linear_stack_free(void *plan);
 /* factor[n] = num / (sA * sB[n]) in the reference's operation order (fp32 multiply, fp32 divide;
  * fully_connected.cpp:396,409): num = 1 for fp32 output, the output scale for u8 output.  d_sA (device
  * scalar) overrides sA, col_scale (device [N]) overrides sB.  factor: device [N]. */
