@@ -72,7 +72,7 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
+        sm, mx, pw, reasons = [], [], [], set()
         for line in out.strip().splitlines():
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
@@ -80,12 +80,14 @@ class ClockSampler:
             try:
                 sm.append(float(f[1]))
                 mx.append(float(f[2]))
+                pw.append(float(f[3]))
             except ValueError:
                 continue
             for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_min_mhz": min(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "power_w": float(np.median(pw)) if pw else None,
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
@@ -162,6 +164,30 @@ def run_reference_arm(args, rank):
 
 
 # ------------------------------------------------------------------------------------ GPU arm
+def check_rows_against_numpy(stack, x, rows):
+    """The step's arithmetic restated with numpy on a few token rows (rows are independent once the
+    dynamic input scale is fixed): F32 -> U8_Q as quantizeF32ToU8 does it, exact integer accumulators,
+    factor[n] = num / (sA * sB[n]) in binary32, u8 = usat8(rne(acc * factor) + 128) between layers, fp32
+    at the end.  Returns True when the device output rows carry the same bits."""
+    sA = np.float32(stack.d_scale[0].item())
+    xr = x.reshape(stack.M, -1)[rows].astype(np.float32)
+    act = np.clip(np.rint((xr * sA).astype(np.float32) + np.float32(128)), 1, 255).astype(np.uint8)
+    last = len(stack.layers) - 1
+    for i, l in enumerate(stack.layers):
+        W = l.Wq_host.astype(np.float64)
+        acc = (act.astype(np.float64) @ W - 128.0 * W.sum(axis=0)[None, :]).astype(np.int64).astype(np.int32)
+        num = np.float32(1.0) if i == last else np.float32(stack.out_scales[i])
+        fac = (num / (sA * l.w_scale_host)).astype(np.float32)
+        f = (acc.astype(np.float32) * fac[None, :]).astype(np.float32)
+        if i == last:
+            got = stack.out_dev.cpu().numpy().reshape(stack.M, -1)[rows]
+            return got.tobytes() == f.tobytes()
+        v = np.rint(f).astype(np.int64) + 128
+        act = np.where((v >= 0) & (v <= 255), v, 255).astype(np.uint8)
+        sA = np.float32(stack.out_scales[i])
+    return False
+
+
 def run_b200_arm(args, rank, world, local_rank):
     import torch
 
@@ -189,6 +215,13 @@ def run_b200_arm(args, rank, world, local_rank):
     out_host = torch.zeros(M_TOKENS * HIDDEN, dtype=torch.float32).pin_memory()
     stack.x_dev.copy_(x_host)
     stack.calibrate()
+    # the timed computation against a CPU computation of the same step, on a sample of token rows
+    stack.step()
+    torch.cuda.synchronize()
+    parity_rows = np.unique(np.linspace(0, M_TOKENS - 1, 24).astype(np.int64))
+    parity_ok = bool(check_rows_against_numpy(stack, x_host.numpy(), parity_rows))
+    if not parity_ok:
+        raise SystemExit("bench.py: the device output differs from the CPU computation on the sampled rows")
     B.CHECK_STATUS(lib.bolt_b200_set_pointer_mode(1))
     flush = torch.zeros(64 << 20, dtype=torch.float32, device="cuda")  # 256 MiB = 2 x L2; fp32 so that sum() only reads
     sink = []
@@ -270,6 +303,28 @@ def run_b200_arm(args, rank, world, local_rank):
     torch.cuda.synchronize()
     e2e_s = max(time.perf_counter() - t0 - flush_s, 1e-9)
     clocks = sampler.stop() if rank == 0 else None
+    # the same step replayed back to back for about two seconds: what the stack sustains under the power limit
+    sustained = None
+    if rank == 0 and world == 1 and g_step is not None and not args.no_sustained:
+        s2 = ClockSampler(local_rank)
+        s2.start()
+        reps, t_s = 0, 0.0
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        wall = time.perf_counter()
+        while time.perf_counter() - wall < 2.0:
+            a.record(stream)
+            for _ in range(200):
+                g_step.replay()
+            b.record(stream)
+            b.synchronize()
+            t_s += a.elapsed_time(b) / 1e3
+            reps += 200
+        c2 = s2.stop()
+        peaks_s, _ = measured_peaks()
+        tops_s = OPS_PER_STEP * reps / t_s / 1e12
+        sustained = {"seconds": t_s, "steps": reps, "tops": tops_s, "ms_per_step": t_s / reps * 1e3,
+                     "frac_of_2x_bf16_sustained": tops_s / (2.0 * peaks_s.get("bf16_tflops_sustained", peaks_s["bf16_tflops"])),
+                     "clocks": c2, "note": "no L2 eviction between steps (weights stay in L2), graph replays back to back"}
     status = lib.bolt_b200_device_status()
 
     vals = torch.tensor([dev_s, gemm_s, e2e_s], dtype=torch.float64, device="cuda")
@@ -300,6 +355,9 @@ def run_b200_arm(args, rank, world, local_rank):
                 "h2d_bytes_per_step": M_TOKENS * HIDDEN * 4, "d2h_bytes_per_step": M_TOKENS * HIDDEN * 4,
                 "ms_per_step": e2e_s / args.steps * 1e3},
         "gpu_launches": int(launches),
+        "parity_checked": parity_ok,
+        "parity_note": "%d of %d token rows of the step's fp32 output compared bit for bit with a numpy "
+                       "restatement of the whole 24-layer chain before timing" % (len(parity_rows), M_TOKENS),
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": gemm_tops, "peak": peak_i8, "unit": "TFLOP/s",
                      "frac": gemm_tops / peak_i8,
@@ -311,6 +369,8 @@ def run_b200_arm(args, rank, world, local_rank):
                      "note": "int8 multiply-add ops (2*M*N*K) in the TFLOP/s slot; peak = 2 x bf16_tflops of "
                              + peak_src + " (no int8 entry in MEASURED_PEAKS.json); nominal dense int8 is 4500"},
     }
+    if sustained is not None:
+        line["sustained"] = sustained
     if base is not None:
         line["cpu_baseline"] = base
     print(json.dumps(line))
@@ -329,8 +389,18 @@ def run_side_workload(args):
         raise SystemExit("bench.py: no CUDA device; there is no CPU fallback")
     B.load(build_if_missing=False)
     peaks, src = measured_peaks()
+    sampler = ClockSampler(0)
+    sampler.start()
     res = workloads.WORKLOADS[args.workload](peaks)
-    res["peaks"] = {"hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"], "source": src}
+    res["clocks"] = sampler.stop()   # sampled every 50 ms over the whole workload, warm-up included
+    mhz = res["clocks"].get("sm_mhz")
+    if mhz:
+        # time x clock, so that runs taken at different clocks can be compared: millions of SM cycles
+        for row in res.get("rows", []):
+            if "ms" in row:
+                row["mcycles_at_median_clock"] = row["ms"] * mhz * 1e-3
+    res["peaks"] = {"hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"],
+                    "bf16_tflops_sustained": peaks.get("bf16_tflops_sustained"), "source": src}
     res["device_status"] = B.lib().bolt_b200_device_status()
     print(json.dumps(res))
 
@@ -342,9 +412,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU leg (profiling runs)")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the two-second back-to-back replay")
     ap.add_argument("--workload", default="bert_stack",
                     help="bert_stack (the headline, default) or one of the side workloads: ffn, gemv, quantize, "
-                         "resnet_conv, bnn (1 GPU, prints that workload's figures as one JSON line)")
+                         "resnet_conv, resnet_conv_u8, bnn, i8_peak (1 GPU, prints that workload's figures as one "
+                         "JSON line with the clocks sampled while it ran)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))

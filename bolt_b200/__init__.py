@@ -91,6 +91,11 @@ class ConvolutionParamSpec(C.Structure):
         (k, C.c_uint32) for k in ("round_mode", "output_pad_t", "output_pad_h", "output_pad_w")]
 
 
+class ConvExt(C.Structure):
+    """bolt_b200_conv_ext"""
+    _fields_ = [("output_scale", C.c_float), ("filter_scales", C.c_void_p)]
+
+
 class GemmEpilogue(C.Structure):
     """bolt_b200_gemm_epilogue"""
     _fields_ = [("out_dt", C.c_uint32), ("accumulate", C.c_int), ("out_scale", C.c_float),
@@ -105,6 +110,8 @@ _TDp = C.POINTER(TensorDesc)
 # name -> (restype, argtypes); every symbol the header declares
 SIGNATURES = {
     "bolt_b200_set_device": (C.c_int, [C.c_int]),
+    "bolt_b200_use_para": (C.c_int, [_vp]),
+    "bolt_b200_i8_mma_rate": (C.c_int, [C.c_uint32, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "bolt_b200_set_stream": (C.c_int, [_vp]),
     "bolt_b200_synchronize": (C.c_int, []),
     "bolt_b200_device_status": (C.c_int, []),
@@ -132,6 +139,8 @@ SIGNATURES = {
     "dequantize_cuda_b200": (C.c_int, [_TDp, _vp, _f32p, _TDp, _vp, _TDp, _vp]),
     "bolt_b200_absmax_scale_f32": (C.c_int, [_vp, C.c_uint64, _vp]),
     "bolt_b200_quantize_f32_u8_noalloc": (C.c_int, [_vp, C.c_uint64, _vp, _vp]),
+    "convolution_infer_output_size_cuda_b200": (
+        C.c_int, [_TDp, _TDp, C.POINTER(ConvolutionParamSpec), _TDp, _u32]),
     "convolution_infer_forward_algorithm_cuda_b200": (
         C.c_int, [_TDp, _TDp, _TDp, C.POINTER(ConvolutionParamSpec), _u32, _u32p, _u32]),
     "convolution_transform_filter_bytes_cuda_b200": (
@@ -143,6 +152,9 @@ SIGNATURES = {
     "convolution_cuda_b200": (
         C.c_int, [_TDp, _vp, _vp, _TDp, _vp, C.POINTER(ConvolutionParamSpec), _u32, _TDp, _vp, _TDp, _vp,
                   _u32, _vp, _TDp, _vp, C.POINTER(ActivationParamSpec)]),
+    "bolt_b200_convolution_ex": (
+        C.c_int, [_TDp, _vp, _vp, _TDp, _vp, C.POINTER(ConvolutionParamSpec), _u32, _TDp, _vp, _TDp, _vp,
+                  _u32, _vp, _TDp, _vp, C.POINTER(ActivationParamSpec), C.POINTER(ConvExt)]),
     "b200_matrix_matrix_multiply_tmp_bytes": (C.c_int, [TensorDesc, TensorDesc, _u32p, _u32]),
     "b200_matrix_matrix_multiply": (
         C.c_int, [TensorDesc, _vp, TensorDesc, _vp, _u32, _vp, TensorDesc, _vp, _f32p, _u32]),
@@ -278,14 +290,10 @@ def conv_param(oc, fh, fw, stride=1, pad=0, dilation=1, relu=False):
 def convolution_infer_output_size(inputDesc, filterDesc, p, target_dt):
     """compute/tensor/src/convolution.cpp:28-145 for the CPU layouts: output format NCHWc16 for a
     u8 target with more than 8 output channels, NCHWc8 otherwise (:98-103)."""
-    iw, ih, ic, n = inputDesc.dims[0], inputDesc.dims[1], inputDesc.dims[2], inputDesc.dims[3]
-    fw, fh, fn = filterDesc.dims[0], filterDesc.dims[1], filterDesc.dims[3]
-    oh = (ih + p.pad_top + p.pad_bottom - ((fh - 1) * p.dilatedRate_h + 1)) // p.stride_h + 1
-    ow = (iw + p.pad_left + p.pad_right - ((fw - 1) * p.dilatedRate_w + 1)) // p.stride_w + 1
-    if fn % 8 != 0:
-        raise BoltError(NOT_SUPPORTED, "convolution_infer_output_size")
-    df = DF_NCHWC16 if (target_dt == DT_U8_Q and fn != 8) else DF_NCHWC8
-    return tensor4df(target_dt, df, n, fn, oh, ow)
+    out = TensorDesc()
+    CHECK_STATUS(lib().convolution_infer_output_size_cuda_b200(C.byref(inputDesc), C.byref(filterDesc), C.byref(p),
+                                                               C.byref(out), target_dt), "convolution_infer_output_size")
+    return out
 
 
 def convolution_infer_forward_algorithm(inputDesc, filterDesc, outputDesc, p, target_dt):
@@ -319,20 +327,30 @@ def convolution_infer_forward_tmp_bytes(inputDesc, ftmDesc, outputDesc, p, alg):
 
 
 def convolution(inputDesc, input_ptr, ftmDesc, filter_ptr, p, alg, scale, bias_ptr, tmp_bytes, tmp_ptr, outputDesc,
-                output_ptr, relu=False, eltwise_ptr=None):
+                output_ptr, relu=False, eltwise_ptr=None, output_scale=None, filter_scales_ptr=None):
     """`scale`: for int8 a 3-float list {input, output, filter} updated in place (convolution_cpu.hpp:142-157);
-    for 1-bit filters a device/host pointer to the fp16 per-channel scales."""
+    for 1-bit filters a device/host pointer to the fp16 per-channel scales.  `relu`: bool, or an activation
+    mode number.  output_scale / filter_scales_ptr: the extension of bolt_b200_convolution_ex."""
     act = ActivationParamSpec()
-    act.mode = ACTIVATION_RELU if relu else ACTIVATION_NULL
+    act.mode = int(relu) if not isinstance(relu, bool) else (ACTIVATION_RELU if relu else ACTIVATION_NULL)
     sd, bd = tensor1d(DT_F32, 3), tensor1d(DT_F32, outputDesc.dims[2])
     if isinstance(scale, list):
         arr = (C.c_float * len(scale))(*scale)
         sp = C.cast(arr, C.c_void_p)
     else:
         arr, sp = None, scale
-    CHECK_STATUS(lib().convolution_cuda_b200(C.byref(inputDesc), input_ptr, eltwise_ptr, C.byref(ftmDesc), filter_ptr,
-                                             C.byref(p), alg, C.byref(sd), sp, C.byref(bd), bias_ptr, tmp_bytes, tmp_ptr,
-                                             C.byref(outputDesc), output_ptr, C.byref(act)), "convolution")
+    if output_scale is None and filter_scales_ptr is None:
+        CHECK_STATUS(lib().convolution_cuda_b200(C.byref(inputDesc), input_ptr, eltwise_ptr, C.byref(ftmDesc), filter_ptr,
+                                                 C.byref(p), alg, C.byref(sd), sp, C.byref(bd), bias_ptr, tmp_bytes, tmp_ptr,
+                                                 C.byref(outputDesc), output_ptr, C.byref(act)), "convolution")
+    else:
+        ext = ConvExt()
+        ext.output_scale = 0.0 if output_scale is None else float(output_scale)
+        ext.filter_scales = filter_scales_ptr
+        CHECK_STATUS(lib().bolt_b200_convolution_ex(C.byref(inputDesc), input_ptr, eltwise_ptr, C.byref(ftmDesc), filter_ptr,
+                                                    C.byref(p), alg, C.byref(sd), sp, C.byref(bd), bias_ptr, tmp_bytes,
+                                                    tmp_ptr, C.byref(outputDesc), output_ptr, C.byref(act), C.byref(ext)),
+                     "convolution_ex")
     if arr is not None:
         for i in range(len(scale)):
             scale[i] = arr[i]

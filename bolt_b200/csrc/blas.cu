@@ -141,6 +141,9 @@ EE run_gemm(U32 N, U32 M, U32 K, bool a_t, const void *A, const void *B, const v
     if (A == nullptr || B == nullptr || C == nullptr) {
         return NULL_POINTER;
     }
+    if (on_other_device(A) || on_other_device(B) || on_other_device(C)) {
+        return NOT_MATCH;  // device memory of a GPU other than the one this thread's calls run on
+    }
     const U32 Np = B200_ALIGN(N, 16), Kp = B200_ALIGN(K, 8);
     const size_t esz = ep.out_kind == 2 ? 1 : 4;
     Stage sg;
@@ -526,6 +529,7 @@ EE b200_matrix_matrix_multiply(TensorDesc aDesc, const void *A, TensorDesc bDesc
         return NOT_SUPPORTED;
     }
     const void *packed = B;
+    bool packed_here = false;
     if (bdf != DF_NKNxKx) {
         U32 rhsBytes = 0;
         B200_EE(matrix_matrix_multiply_transform_rhs_bytes_cuda_b200(bN, bK, bdt, bdf, nullptr, &rhsBytes));
@@ -535,12 +539,19 @@ EE b200_matrix_matrix_multiply(TensorDesc aDesc, const void *A, TensorDesc bDesc
         TensorDesc packedDesc;
         B200_EE(matrix_matrix_multiply_transform_rhs_cuda_b200(&bDesc, B, &packedDesc, tmp));
         packed = tmp;
+        packed_here = true;
         tmp = reinterpret_cast<char *>(tmp) + rhsBytes;  // offsetC sits there (mmm.cpp:217-218)
     }
     if (cdt == DT_I32) {
         scale = nullptr;  // mmm.cpp:222-224
     }
-    return mmm_cuda_b200(cN, cM, aK, bdt, adf, A, packed, tmp, C, scale);
+    const EE ret = mmm_cuda_b200(cN, cM, aK, bdt, adf, A, packed, tmp, C, scale);
+    if (packed_here && !is_device_ptr(packed)) {
+        // the caller's scratch is not a weight: its device copy served this call only (a later call may
+        // put other bytes at the same host address)
+        bolt_b200_release_weight(packed);
+    }
+    return ret;
 }
 
 EE b200_matrix_vector_multiply_tmp_bytes(TensorDesc mDesc, TensorDesc vDesc, U32 *bytes, Arch arch)
@@ -635,7 +646,12 @@ EE b200_matrix_vector_multiply(TensorDesc mDesc, const void *matrix, TensorDesc 
             &mDesc, matrix, &packedDesc, reinterpret_cast<char *>(tmp) + (size_t)rlen * 4, tmp));
         dataB = tmp;
     }
-    return mvm_cuda_b200(row, col, mdt, mdf, dataB, vector, result, tmp, scale);
+    const EE ret = mvm_cuda_b200(row, col, mdt, mdf, dataB, vector, result, tmp, scale);
+    if (dataB == tmp && !is_device_ptr(tmp)) {
+        // the caller's scratch is not a weight: drop the device copy made while packing into it
+        bolt_b200_release_weight(reinterpret_cast<char *>(tmp) + (size_t)rlen * 4);
+    }
+    return ret;
 }
 
 }  // extern "C"

@@ -224,6 +224,12 @@ EE bnn_geometry(const TensorDesc *inputDesc, const TensorDesc *filterDesc, const
     g->Cw = (g->f.c + 31) / 32;
     g->taps = g->f.h * g->f.w;
     g->xb_bytes = (size_t)g->in.n * g->Hp * g->Wp * g->Cw * 4;
+    // the output geometry must be the one the input, filter and padding give: the kernel reads the padded
+    // bit tensor at (oh * stride + kh, ow * stride + kw) without further checks
+    if (g->f.h == 0 || g->f.w == 0 || g->Hp < g->f.h || g->Wp < g->f.w || g->out.n != g->in.n ||
+        g->out.h != (g->Hp - g->f.h) / g->sH + 1 || g->out.w != (g->Wp - g->f.w) / g->sW + 1) {
+        return NOT_MATCH;
+    }
     return SUCCESS;
 }
 

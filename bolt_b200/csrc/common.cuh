@@ -56,11 +56,11 @@ struct WeightTwin {
 
 // kernel families whose dynamic shared-memory limit has to be raised above 48 KiB; the attribute
 // belongs to the device that is current when it is set, so it is remembered per device context
-enum KernelFamily { KF_GEMM = 0, KF_CONV, KF_GEMV, KF_GEMV_ROW, KF_BNN, KF_COUNT };
+enum KernelFamily { KF_GEMM = 0, KF_CONV, KF_GEMV, KF_GEMV_ROW, KF_BNN, KF_PROBE, KF_COUNT };
 
 struct DeviceCtx {
     int device = 0;
-    bool smem_raised[KF_COUNT] = {false, false, false, false, false};
+    bool smem_raised[KF_COUNT] = {};
     std::mutex attr_mu;
     int max_pairs = -1;  // co-resident 2-CTA clusters of the tensor-core GEMM (-1: not queried yet)
     int sm_count = 148;
@@ -78,7 +78,7 @@ struct DeviceCtx {
 };
 
 struct ThreadState {
-    int device = 0;
+    int device = -1;  // -1: not chosen through bolt_b200_set_device -- follow the thread's current CUDA device
     cudaStream_t stream = nullptr;
     bool device_only = false;
     int last_gemm_tc = 0;
@@ -98,6 +98,8 @@ EE raise_smem_limit(DeviceCtx *c, KernelFamily f, const void *const *kernels, in
 
 // true if p is memory the GPU can dereference (device or managed)
 bool is_device_ptr(const void *p);
+// true if p is plain device memory of a GPU other than the one this thread's calls run on
+bool on_other_device(const void *p);
 
 // Staging helper for one call: maps caller pointers to device pointers.  Host inputs are
 // copied into the workspace; host outputs get a workspace buffer that finish() copies back.

@@ -36,9 +36,27 @@ EE cuda_ee(cudaError_t e)
 
 DeviceCtx *ctx()
 {
+    // The device chosen with bolt_b200_set_device, else the CUDA device that is current in this thread (a
+    // caller that manages devices itself -- one rank per GPU under torch.distributed -- is followed, not
+    // overridden).
     int dev = tls().device;
+    if (dev < 0 && cudaGetDevice(&dev) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
     if (dev < 0 || dev >= kMaxDevices) {
         return nullptr;
+    }
+    {
+        // fast path: the context exists and its device is current
+        DeviceCtx *c = __atomic_load_n(&g_ctx[dev], __ATOMIC_ACQUIRE);
+        if (c != nullptr) {
+            int cur = -1;
+            if (cudaGetDevice(&cur) != cudaSuccess || cur != dev) {
+                cudaSetDevice(dev);
+            }
+            return c;
+        }
     }
     std::lock_guard<std::mutex> g(g_ctx_mu);
     if (g_ctx[dev] == nullptr) {
@@ -59,7 +77,7 @@ DeviceCtx *ctx()
         }
         c->d_scratch_u = reinterpret_cast<unsigned *>(c->d_scratch);
         cudaMemset(c->d_scratch, 0, 4096);
-        g_ctx[dev] = c;
+        __atomic_store_n(&g_ctx[dev], c, __ATOMIC_RELEASE);
     } else {
         int cur = -1;
         if (cudaGetDevice(&cur) != cudaSuccess || cur != dev) {
@@ -96,6 +114,27 @@ bool is_device_ptr(const void *p)
         return false;
     }
     return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+bool on_other_device(const void *p)
+{
+    if (p == nullptr || tls().device_only) {
+        return false;
+    }
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    if (a.type != cudaMemoryTypeDevice) {
+        return false;
+    }
+    int dev = tls().device;
+    if (dev < 0 && cudaGetDevice(&dev) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return a.device != dev;
 }
 
 // ---- Stage -----------------------------------------------------------------------------------
@@ -210,6 +249,18 @@ EE bolt_b200_set_device(int device)
     }
     tls().device = device;
     return ctx() ? SUCCESS : UNKNOWN;
+}
+
+EE bolt_b200_use_para(const bolt_b200_para *para)
+{
+    if (para == nullptr) {
+        tls().device = -1;
+        tls().stream = nullptr;
+        return SUCCESS;
+    }
+    B200_EE(bolt_b200_set_device(para->device));
+    tls().stream = reinterpret_cast<cudaStream_t>(para->stream);
+    return SUCCESS;
 }
 
 EE bolt_b200_set_stream(void *cuda_stream)

@@ -5,18 +5,30 @@
 // Replaces Bolt's AVX512 direct and 1x1 convolution kernels and their drivers
 // (compute/tensor/src/cpu/x86/int8/avx512/convolution_direct.cpp:2584-2809,
 //  convolution_1x1_direct.cpp:2073-2327), the filter transform
-// (cpu/x86/int8/convolution_transform.cpp:18-238) and the input pad / relayout
-// (cpu/x86/int8/transform_functions_int8.h:19-224).
+// (cpu/x86/int8/convolution_transform.cpp:18-238), the bias / offset fold
+// (cpu/x86/quantize.cpp:64-121) and the input pad / relayout (cpu/x86/int8/transform_functions_int8.h:19-224).
 //
-// GEMM view: M = output pixels (a TH x TW patch of one image = 128 rows per tile), N = output
-// channels, K = (kh, kw, input-channel block of 16).  The input is brought to a padded
-// channels-of-16 layout [N][IC/16][Hp][Wp][16] (pad value 128, one streaming pass; skipped when
-// the caller's tensor already has it).  There a 16-byte K chunk of 128 pixels is exactly a 5-D TMA
-// box {16 B, TW, TH, chunks, 1} -- element strides carry the convolution stride, the start
-// coordinates carry (kh, kw) -- and lands in shared memory as 8-row x 16-byte core matrices, the
-// un-swizzled K-major operand layout of tcgen05.mma.  No im2col buffer ever exists.  Weights are
-// pre-packed [OC][K] and loaded like the GEMM's B operand (128-byte swizzle).  Warp roles, the
-// tensor-memory double buffering and the bounded waits are those of gemm_i8_tcgen05.cu.
+// GEMM view: M = output pixels, N = output channels, K = (kh, kw, input-channel block of 16).  A tile is a
+// TW x TH patch of TN images (at most 128 pixels).  On a channels-of-16 tensor [N][IC/16][H][W][16] a
+// 16-byte K chunk of such a tile is one TMA box -- element strides carry the convolution stride, the start
+// coordinates carry (kh, kw) and the padding -- and lands in shared memory as 8-row x 16-byte core
+// matrices, the un-swizzled K-major operand layout of tcgen05.mma.  No im2col buffer ever exists.
+//
+// Padding without a padded copy: taps outside the image are filled with 0 by TMA where the reference
+// fills 128, so   offsetC + sum_all W*X(pad 128)  =  sum_valid W*X - 128 * sum_valid W.   The filter
+// transform leaves per-tap weight sums behind the packed filter; the pixels of a tile fall into a few
+// border classes (which kh, which kw are inside), and the epilogue adds the offset of its pixel's class.
+// Integer arithmetic, so the result is the reference's bit for bit.  Inputs that are not NCHWc16 with
+// a multiple of 16 channels are first brought to that layout (pad value 128, one streaming pass).
+//
+// 1x1 / stride 1 / unpadded layers are run as images of one row of H*W pixels: tiles of 16 pixels x 8
+// images fill all 128 rows and move 256 contiguous bytes per TMA row.
+//
+// The bias / offset fold (round(bias*scaleO) + offsetC) and the conversion factors (one per tensor, or
+// one per output channel) are computed by the epilogue warps when they stage a column block's
+// constants; one launch per call.  Weights are pre-packed [OC][K] and loaded like the GEMM's B operand
+// (128-byte swizzle).  Warp roles, the tensor-memory double buffering and the bounded waits are those of
+// gemm_i8_tcgen05.cu.
 #include <cstring>
 
 #include "common.cuh"
@@ -35,7 +47,9 @@ constexpr int NUM_THREADS = 64 + EPI_THREADS;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int SMEM_A_STAGE = BLOCK_M * BLOCK_K;      // 8 K-chunks x 128 pixels x 16 B
 constexpr int SMEM_B_STAGE = MAX_BLOCK_N * BLOCK_K;
-constexpr int CHUNK_BYTES = BLOCK_M * 16;            // one 16-byte K chunk of all 128 pixels
+constexpr int MAX_CLASSES = 16;                      // border classes of a layer (3 x 3 pad 1: 9)
+constexpr int MAX_AXIS_CLASSES = 8;
+constexpr int CLASS_PITCH = MAX_BLOCK_N + 4;         // int32 per class row; +4 staggers the banks of different classes
 
 struct __align__(16) SmemCtl {
     uint64_t full[STAGES];
@@ -44,27 +58,40 @@ struct __align__(16) SmemCtl {
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
-    __align__(16) int32_t offs[2048];  // offsetC + bias of every output channel (layers with OC <= 2048)
+    // constants of the column block being worked on: per border class the offset of every channel
+    // (offsetC-like term + round(bias * scaleO)), and the conversion factor of every channel
+    __align__(16) int32_t offs[MAX_CLASSES * CLASS_PITCH];
+    __align__(16) float colf[MAX_BLOCK_N];
 };
 
 constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * (SMEM_A_STAGE + SMEM_B_STAGE) + sizeof(SmemCtl);
 
 struct ConvParams {
     uint32_t N, OH, OW, OC;
-    uint32_t TW, TH, tw_shift, tiles_w, tiles_h;
-    uint32_t ICb, FW;
+    uint32_t TW, TH, TN, tiles_w, tiles_h, tiles_n_img;   // tile = TW x TH pixels of TN images
+    uint32_t rows;          // TW * TH * TN <= 128: pixels of a tile = rows of the A operand
+    uint32_t ICb, FW, FH;
     uint32_t sH, sW, dH, dW;
+    int32_t pt, pl;         // padding folded into the TMA start coordinates (0 when the input was copied padded)
     uint32_t G;             // K chunks per TMA load: divides both ICb and 8
-    uint32_t merged_w;      // 1: stride-1 rows, map_x is 4-D with (c16, w) merged into one byte dimension
+    uint32_t merged_w;      // 1: stride-1 rows, (c16, w) merged into one byte dimension
     uint32_t total_chunks;  // taps * ICb
     uint32_t num_kb;        // ceil(total_chunks / 8)
     uint32_t block_n, tiles_n, tiles_m;
     void *out;
     const float *eltwise;
-    const int32_t *offs;    // [OC]: offsetC + round(bias * scaleO)
-    float factor;           // 1 / scaleO (fp32 output) or outScale / scaleO (fused u8 output)
+    const int32_t *offsetC; // [OC]: -128 * sum of the filter
+    const int32_t *tapsum;  // [OC][taps]: sum over input channels of every tap (border classes), or null
+    const float *bias;      // [OC] or null
+    const float *fscale;    // [OC] per-output-channel filter scales, or null (then sF)
+    float sI, sF, num;      // scaleO = sI * sF; factor = num / scaleO (num 1: fp32 out; output scale: fused u8)
     int relu;
     int *status;
+    // border classes: class = row_class * n_cc + col_class; class 0 has every tap inside
+    uint32_t n_rc, n_cc;
+    uint8_t rc_lo[MAX_AXIS_CLASSES], rc_hi[MAX_AXIS_CLASSES];   // valid kh range [lo, hi] of a row class
+    uint8_t cc_lo[MAX_AXIS_CLASSES], cc_hi[MAX_AXIS_CLASSES];
+    uint8_t row_class[256], col_class[256];                      // per output row / column
 };
 
 // KIND 1: fp32 output (dequantize, + eltwise, ReLU).  KIND 0: int32 output after ReLU, the staging
@@ -72,8 +99,8 @@ struct ConvParams {
 // output scale, the arithmetic of quantizeI32ToU8 with both scales given (avx512/quantize.cpp:372-414:
 // vcvtdq2ps, vmulps, vaddps 128, vcvtps2dq, vpmovusdb) fused behind the ReLU.
 template <int KIND>
-__device__ __forceinline__ void store_block16(const ConvParams &p, const int32_t *offs, size_t base, uint32_t width,
-    const uint32_t *r /*16 accumulators*/)
+__device__ __forceinline__ void store_block16(const ConvParams &p, const int32_t *offs, const float *colf, size_t base,
+    uint32_t width, const uint32_t *r /*16 accumulators*/)
 {
     if (KIND == 2) {
         uint8_t *out = reinterpret_cast<uint8_t *>(p.out) + base;
@@ -81,12 +108,14 @@ __device__ __forceinline__ void store_block16(const ConvParams &p, const int32_t
 #pragma unroll
         for (int j = 0; j < 16; j += 4) {
             const int4 o = *reinterpret_cast<const int4 *>(offs + j);
+            const float4 c4 = *reinterpret_cast<const float4 *>(colf + j);
+            const float cf[4] = {c4.x, c4.y, c4.z, c4.w};
             int v[4] = {(int)r[j] + o.x, (int)r[j + 1] + o.y, (int)r[j + 2] + o.z, (int)r[j + 3] + o.w};
             uint32_t b[4];
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
                 const int a = p.relu ? max(v[t], 0) : v[t];
-                const float f = __fadd_rn(__fmul_rn(__int2float_rn(a), p.factor), 128.0f);
+                const float f = __fadd_rn(__fmul_rn(__int2float_rn(a), cf[t]), 128.0f);
                 // rne(f) as unsigned, clamped at 255: negatives wrap above 255 like vpmovusdb reads them
                 b[t] = min(__float_as_uint(__fadd_rn(f, 12582912.0f)) - 0x4B400000u, 255u);
             }
@@ -103,8 +132,9 @@ __device__ __forceinline__ void store_block16(const ConvParams &p, const int32_t
         for (int j = 0; j < 16; j += 4) {
             if ((uint32_t)j < width) {
                 const int4 o = *reinterpret_cast<const int4 *>(offs + j);
-                float4 v = make_float4(acc_to_f32((int)r[j] + o.x, p.factor), acc_to_f32((int)r[j + 1] + o.y, p.factor),
-                    acc_to_f32((int)r[j + 2] + o.z, p.factor), acc_to_f32((int)r[j + 3] + o.w, p.factor));
+                const float4 c4 = *reinterpret_cast<const float4 *>(colf + j);
+                float4 v = make_float4(acc_to_f32((int)r[j] + o.x, c4.x), acc_to_f32((int)r[j + 1] + o.y, c4.y),
+                    acc_to_f32((int)r[j + 2] + o.z, c4.z), acc_to_f32((int)r[j + 3] + o.w, c4.w));
                 if (p.eltwise != nullptr) {
                     const float4 e = *reinterpret_cast<const float4 *>(p.eltwise + base + j);
                     v.x = __fadd_rn(v.x, e.x);
@@ -143,7 +173,7 @@ __device__ __forceinline__ void store_block16(const ConvParams &p, const int32_t
 template <int KIND>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-    const ConvParams p)
+    const __grid_constant__ ConvParams p)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -154,15 +184,18 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t num_tiles = p.tiles_m * p.tiles_n;
+    const uint32_t chunk_bytes = p.rows * 16;   // one 16-byte K chunk of all the tile's pixels
 
     if (threadIdx.x == 0) {
+        prefetch_tensormap(&map_x);
+        prefetch_tensormap(&map_w);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&ctl->full[s], 1);
             mbar_init(&ctl->empty[s], 1);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&ctl->tmem_full[a], 1);
-            mbar_init(&ctl->tmem_empty[a], EPI_THREADS);
+            mbar_init(&ctl->tmem_empty[a], EPI_WARPS);
         }
         ctl->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -179,13 +212,14 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     tcgen05_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
 
-    // tile -> (image, patch origin, first output channel)
+    // tile -> (first image, patch origin, first output channel)
     auto decode = [&](uint32_t tile, uint32_t &n, uint32_t &oh0, uint32_t &ow0, uint32_t &n0) {
         const uint32_t mt = tile % p.tiles_m;
         n0 = (tile / p.tiles_m) * p.block_n;
-        const uint32_t per_img = p.tiles_w * p.tiles_h;
-        n = mt / per_img;
-        const uint32_t r = mt - n * per_img;
+        const uint32_t per_grp = p.tiles_w * p.tiles_h;
+        const uint32_t g = mt / per_grp;
+        n = g * p.TN;
+        const uint32_t r = mt - g * per_grp;
         oh0 = (r / p.tiles_w) * p.TH;
         ow0 = (r % p.tiles_w) * p.TW;
     };
@@ -205,20 +239,21 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                     }
                     const uint32_t q0 = kb * 8;
                     const uint32_t nq = min(8u, p.total_chunks - q0);
-                    mbar_expect_tx(&ctl->full[stage], nq * CHUNK_BYTES + p.block_n * BLOCK_K);
+                    mbar_expect_tx(&ctl->full[stage], nq * chunk_bytes + p.block_n * BLOCK_K);
                     for (uint32_t j = 0; j < nq; j += p.G) {
                         const uint32_t q = q0 + j;
                         const uint32_t tap = q / p.ICb;
                         const uint32_t cb = q - tap * p.ICb;
                         const uint32_t kh = tap / p.FW, kw = tap - kh * p.FW;
-                        uint8_t *dst = smem_a + stage * SMEM_A_STAGE + j * CHUNK_BYTES;
+                        uint8_t *dst = smem_a + stage * SMEM_A_STAGE + j * chunk_bytes;
+                        // taps outside the image start at negative or too large coordinates and read zeros
+                        const int x = (int)(ow0 * p.sW + kw * p.dW) - p.pl;
+                        const int y = (int)(oh0 * p.sH + kh * p.dH) - p.pt;
                         if (p.merged_w) {
                             // a row of TW pixels is TW * 16 contiguous bytes: one wide request per row
-                            tma_load_4d(&map_x, &ctl->full[stage], dst, (int)((ow0 + kw * p.dW) * 16),
-                                (int)(oh0 * p.sH + kh * p.dH), (int)cb, (int)n);
+                            tma_load_4d(&map_x, &ctl->full[stage], dst, x * 16, y, (int)n, (int)cb);
                         } else {
-                            tma_load_5d(&map_x, &ctl->full[stage], dst, 0, (int)(ow0 * p.sW + kw * p.dW),
-                                (int)(oh0 * p.sH + kh * p.dH), (int)cb, (int)n);
+                            tma_load_5d(&map_x, &ctl->full[stage], dst, 0, x, y, (int)n, (int)cb);
                         }
                     }
                     tma_load_2d(&map_w, &ctl->full[stage], smem_b + stage * SMEM_B_STAGE, (int)(kb * BLOCK_K), (int)n0);
@@ -260,9 +295,10 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                     const uint32_t a_addr = smem_u32(smem_a + stage * SMEM_A_STAGE);
                     const uint64_t db = make_desc_sw128(smem_u32(smem_b + stage * SMEM_B_STAGE));
                     for (uint32_t k = 0; 2 * k < nq; ++k) {
-                        // A: two 16-byte K chunks per MMA, CHUNK_BYTES apart; 8-pixel groups 128 B apart.
-                        // An odd last chunk pairs with stale bytes, which meet zero weights.
-                        const uint64_t da = make_desc_noswizzle(a_addr + k * 2 * CHUNK_BYTES, CHUNK_BYTES, 128);
+                        // A: two 16-byte K chunks per MMA, chunk_bytes apart; 8-pixel groups 128 B apart.  Rows
+                        // beyond the tile's pixels read the next chunk's bytes: their accumulators are never
+                        // stored.  An odd last chunk pairs with stale bytes, which meet zero weights.
+                        const uint64_t da = make_desc_noswizzle(a_addr + k * 2 * chunk_bytes, chunk_bytes, 128);
                         umma_i8(tmem_d, da, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
                     }
                     tcgen05_commit(&ctl->empty[stage]);
@@ -288,26 +324,65 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         const uint32_t half = (warp - 2) >> 2;
         const uint32_t et = threadIdx.x - 64;
         const uint32_t nch = p.block_n >> 5;
-        // Per-channel offsets: staged once per CTA when they fit, so that no tile waits on a global
-        // load or a CTA-wide barrier; wider layers read them through L1.
-        const int32_t *offs_all = p.offs;
-        if (p.OC <= 2048) {
-            for (uint32_t i = et; i < 2048; i += EPI_THREADS) {
-                ctl->offs[i] = (i < p.OC) ? p.offs[i] : 0;
-            }
-            asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
-            offs_all = ctl->offs;
-        }
+        const uint32_t n_classes = p.n_rc * p.n_cc;
+        const uint32_t taps = p.FH * p.FW;
         const uint32_t c_begin = half ? ((nch + 1) >> 1) : 0u;
         const uint32_t c_end = half ? nch : ((nch + 1) >> 1);
+        uint32_t staged_n0 = 0xFFFFFFFFu;
         uint32_t it = 0;
+        // After a bounded wait ran out somewhere the warp keeps walking the tiles without touching them:
+        // the named barriers below have to be reached by every epilogue warp the same number of times.
+        bool dead = false;
         for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
             const uint32_t acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
-            uint32_t n, oh0, ow0, n0;
-            decode(tile, n, oh0, ow0, n0);
+            uint32_t n_first, oh0, ow0, n0;
+            decode(tile, n_first, oh0, ow0, n0);
             if (*reinterpret_cast<volatile uint32_t *>(&ctl->abort_flag) != 0) {
-                break;  // some role's bounded wait ran out
+                dead = true;
+            }
+            if (n0 != staged_n0) {
+                // Constants of this column block (tiles run row-block fastest, so this happens tiles_n times
+                // per CTA): conversion factor and, per border class, the integer offset of every channel.
+                asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");  // everyone is done with the old ones
+                for (uint32_t j = et; !dead && j < p.block_n; j += EPI_THREADS) {
+                    const uint32_t oc = n0 + j;
+                    float factor = 0.f;
+                    int boff = 0;
+                    if (oc < p.OC) {
+                        // scaleO = scaleI * scaleF (convolution_direct.cpp:2687), factor = 1 / scaleO (:2699)
+                        const float so = __fmul_rn(p.sI, p.fscale ? p.fscale[oc] : p.sF);
+                        factor = __fdiv_rn(p.num, so);
+                        if (p.bias != nullptr) {
+                            boff = (int)roundf(__fmul_rn(p.bias[oc], so));  // avx512/quantize.cpp:259-266
+                        }
+                    }
+                    ctl->colf[j] = factor;
+                    for (uint32_t cls = 0; cls < n_classes; ++cls) {
+                        int v = 0;
+                        if (oc < p.OC) {
+                            if (cls == 0) {
+                                v = p.offsetC[oc];
+                            } else {
+                                const uint32_t rc = cls / p.n_cc, cc = cls - rc * p.n_cc;
+                                int sum = 0;
+                                for (uint32_t kh = p.rc_lo[rc]; kh <= p.rc_hi[rc] && kh < p.FH; ++kh) {
+                                    for (uint32_t kw = p.cc_lo[cc]; kw <= p.cc_hi[cc] && kw < p.FW; ++kw) {
+                                        sum += p.tapsum[(size_t)oc * taps + kh * p.FW + kw];
+                                    }
+                                }
+                                v = -128 * sum;
+                            }
+                        }
+                        ctl->offs[cls * CLASS_PITCH + j] = v + boff;
+                    }
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+                staged_n0 = n0;
+            }
+            dead = __any_sync(0xffffffffu, dead);
+            if (dead) {
+                continue;
             }
             bool ok = mbar_wait(&ctl->tmem_full[acc], acc_phase);
             ok = __all_sync(0xffffffffu, ok);
@@ -316,25 +391,45 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                     atomicExch(p.status, 13);
                     atomicExch(&ctl->abort_flag, 1u);
                 }
-                break;
+                dead = true;
+                continue;
             }
             tcgen05_fence_after();
+            // this lane's pixel
             const uint32_t r = quad * 32 + lane;
-            const uint32_t oh = oh0 + (r >> p.tw_shift);
-            const uint32_t ow = ow0 + (r & (p.TW - 1));
-            const bool row_ok = oh < p.OH && ow < p.OW;
+            const uint32_t per_img = p.TH * p.TW;
+            const uint32_t nl = r / per_img;
+            const uint32_t rem = r - nl * per_img;
+            const uint32_t th = rem / p.TW;
+            const uint32_t oh = oh0 + th;
+            const uint32_t ow = ow0 + (rem - th * p.TW);
+            const uint32_t n = n_first + nl;
+            const bool row_ok = r < p.rows && n < p.N && oh < p.OH && ow < p.OW;
             const size_t pix = (size_t)oh * p.OW + ow;
             const size_t plane = (size_t)p.OH * p.OW;
+            uint32_t cls = 0;
+            if (row_ok && n_classes > 1) {
+                cls = (uint32_t)p.row_class[oh] * p.n_cc + p.col_class[ow];
+            }
+            const int32_t *offs_px = ctl->offs + cls * CLASS_PITCH;
             const uint32_t tbase = tmem_base + ((quad * 32u) << 16) + acc * MAX_BLOCK_N;
+            auto release = [&]() {
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&ctl->tmem_empty[acc]);
+                }
+            };
             auto emit = [&](uint32_t c, const uint32_t *rr) {
                 if (row_ok) {
 #pragma unroll
                     for (int hb = 0; hb < 2; ++hb) {
-                        const uint32_t ocb = n0 + c * 32 + hb * 16;
+                        const uint32_t col = c * 32 + hb * 16;
+                        const uint32_t ocb = n0 + col;
                         if (ocb < p.OC) {
                             const uint32_t width = min(16u, p.OC - ocb);
                             const size_t base = ((size_t)n * p.OC + ocb) * plane + pix * width;
-                            store_block16<KIND>(p, offs_all + ocb, base, width, rr + hb * 16);
+                            store_block16<KIND>(p, offs_px + col, ctl->colf + col, base, width, rr + hb * 16);
                         }
                     }
                 }
@@ -351,8 +446,7 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                 if (has1) {
                     tmem_ld32(tbase + (c + 1) * 32, rb);
                 } else {
-                    tcgen05_fence_before();
-                    mbar_arrive(&ctl->tmem_empty[acc]);
+                    release();
                 }
                 emit(c, ra);
                 if (has1) {
@@ -360,15 +454,13 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                     if (c + 2 < c_end) {
                         tmem_ld32(tbase + (c + 2) * 32, ra);
                     } else {
-                        tcgen05_fence_before();
-                        mbar_arrive(&ctl->tmem_empty[acc]);
+                        release();
                     }
                     emit(c + 1, rb);
                 }
             }
             if (c_begin >= c_end) {
-                tcgen05_fence_before();
-                mbar_arrive(&ctl->tmem_empty[acc]);
+                release();
             }
         }
     }
@@ -388,34 +480,39 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
 }
 
 // ---- filter packing: s8 NCHW [OC][IC][FH][FW] -> [OCr][K], k = ((kh*FW + kw)*ICb + cb)*16 + c ------------
-// offsetC[oc] = -128 * sum of the filter (convolution_transform.cpp: offsetC first, then the weights).
+// offsetC[oc] = -128 * sum of the filter (convolution_transform.cpp: offsetC first, then the weights);
+// tapsum[oc][tap] = sum over the input channels of one tap (what the border classes are built from).
 __global__ void pack_conv_filter_kernel(const int8_t *__restrict__ src, uint32_t OC, uint32_t IC, uint32_t taps,
-    uint32_t ICb, uint32_t OCr, int8_t *__restrict__ dst, int32_t *__restrict__ offsetC)
+    uint32_t ICb, uint32_t OCr, int8_t *__restrict__ dst, int32_t *__restrict__ offsetC, int32_t *__restrict__ tapsum)
 {
     const uint32_t oc = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const uint32_t lane = threadIdx.x & 31;
     if (oc >= OCr) {
         return;
     }
-    const uint32_t K = taps * ICb * 16;
-    int32_t sum = 0;
-    for (uint32_t k = lane; k < K; k += 32) {
-        const uint32_t c = k & 15, q = k >> 4;
-        const uint32_t tap = q / ICb, cb = q - tap * ICb;
-        const uint32_t ic = cb * 16 + c;
-        int8_t v = 0;
-        if (oc < OC && ic < IC) {
-            v = src[((size_t)oc * IC + ic) * taps + tap];
+    const uint32_t per_tap = ICb * 16;
+    int32_t total = 0;
+    for (uint32_t tap = 0; tap < taps; ++tap) {
+        int32_t sum = 0;
+        for (uint32_t i = lane; i < per_tap; i += 32) {
+            int8_t v = 0;
+            if (oc < OC && i < IC) {
+                v = src[((size_t)oc * IC + i) * taps + tap];
+            }
+            dst[(size_t)oc * taps * per_tap + (size_t)tap * per_tap + i] = v;
+            sum += v;
         }
-        dst[(size_t)oc * K + k] = v;
-        sum += v;
-    }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        for (int o = 16; o > 0; o >>= 1) {
+            sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        }
+        if (lane == 0 && oc < OC) {
+            tapsum[(size_t)oc * taps + tap] = sum;
+        }
+        total += sum;
     }
     if (lane == 0 && oc < OC) {
-        offsetC[oc] = sum * (-128);
+        offsetC[oc] = total * (-128);
     }
 }
 
@@ -471,19 +568,6 @@ __global__ void pad_relayout_kernel(const uint8_t *__restrict__ in, uint32_t N, 
     }
 }
 
-// offs[oc] = round(bias[oc] * scaleO) + offsetC[oc]   (cpu/x86/int8/avx512/quantize.cpp:259-266)
-__global__ void conv_bias_offset_kernel(const float *bias, const int32_t *offsetC, uint32_t n, float scaleO, int32_t *out)
-{
-    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) {
-        int b = 0;
-        if (bias != nullptr) {
-            b = (int)roundf(__fmul_rn(bias[i], scaleO));
-        }
-        out[i] = b + offsetC[i];
-    }
-}
-
 struct Conv4d {
     DataType dt;
     DataFormat df;
@@ -526,9 +610,55 @@ struct ConvGeom {
     Conv4d in, f, out;
     uint32_t sH, sW, dH, dW, pt, pb, pl, pr;
     uint32_t ICb, Hp, Wp, taps, K, OCr;
-    bool needs_copy;
+    bool needs_copy;     // the input has to be brought to the padded channels-of-16 layout first
     size_t xp_bytes;
 };
+
+// Border classes along one axis: output positions grouped by the range of filter taps that fall inside
+// the image.  Returns the number of classes (class 0 = every tap inside), 0 if there are too many or
+// some position has no tap inside at all.
+uint32_t axis_classes(uint32_t out_len, uint32_t in_len, uint32_t f, uint32_t stride, uint32_t dil, uint32_t pad,
+    uint8_t *lo, uint8_t *hi, uint8_t *cls_of)
+{
+    if (out_len > 256 || f > 255) {
+        return 0;
+    }
+    uint32_t n = 1;
+    lo[0] = 0;
+    hi[0] = (uint8_t)(f - 1);
+    for (uint32_t o = 0; o < out_len; ++o) {
+        int first = -1, last = -1;
+        for (uint32_t k = 0; k < f; ++k) {
+            const long pos = (long)o * stride + (long)k * dil - (long)pad;
+            if (pos >= 0 && pos < (long)in_len) {
+                if (first < 0) {
+                    first = (int)k;
+                }
+                last = (int)k;
+            }
+        }
+        if (first < 0) {
+            return 0;
+        }
+        // the taps inside must be one contiguous range (they are: positions grow with k)
+        uint32_t c = 0;
+        for (; c < n; ++c) {
+            if (lo[c] == first && hi[c] == last) {
+                break;
+            }
+        }
+        if (c == n) {
+            if (n == MAX_AXIS_CLASSES) {
+                return 0;
+            }
+            lo[n] = (uint8_t)first;
+            hi[n] = (uint8_t)last;
+            ++n;
+        }
+        cls_of[o] = (uint8_t)c;
+    }
+    return n;
+}
 
 EE conv_geometry(const TensorDesc *inputDesc, const TensorDesc *filterDesc, const TensorDesc *outputDesc,
     const ConvolutionParamSpec *cp, ConvGeom *g)
@@ -553,18 +683,31 @@ EE conv_geometry(const TensorDesc *inputDesc, const TensorDesc *filterDesc, cons
     g->taps = g->f.h * g->f.w;
     g->K = g->taps * g->ICb * 16;
     g->OCr = B200_ALIGN(g->f.n, 8);
-    g->needs_copy = !(g->in.df == DF_NCHWC16 && (g->in.c % 16) == 0 && g->pt == 0 && g->pb == 0 && g->pl == 0 && g->pr == 0);
+    // the output geometry must be the one the input, filter and padding give (convolution.cpp:60-66)
+    const uint32_t eh = (g->f.h - 1) * g->dH + 1, ew = (g->f.w - 1) * g->dW + 1;
+    if (g->Hp < eh || g->Wp < ew || g->out.n != g->in.n || g->out.h != (g->Hp - eh) / g->sH + 1 ||
+        g->out.w != (g->Wp - ew) / g->sW + 1) {
+        return NOT_MATCH;
+    }
+    g->needs_copy = !(g->in.df == DF_NCHWC16 && (g->in.c % 16) == 0);
     g->xp_bytes = (size_t)g->in.n * g->ICb * g->Hp * g->Wp * 16;
     return SUCCESS;
 }
 
-}  // namespace
+struct ConvLaunch {
+    const uint8_t *x;        // [N][ICb][H][W][16]
+    uint32_t H, W;           // extents of x (padded extents after a padded copy)
+    int32_t pt, pl;          // padding still to be applied through the TMA coordinates
+    const int8_t *w;         // [OCr][K]
+    const int32_t *offsetC, *tapsum;
+    const float *bias, *fscale, *eltwise;
+    float sI, sF, num;
+    void *out;
+    int out_kind, relu;
+};
 
-// run the implicit-GEMM kernel; xp: [N][ICb][Hp][Wp][16] u8, w: [OCr][K] s8, offs: [OC] int32 (all device)
-EE launch_conv_tcgen05(const uint8_t *xp, const int8_t *w, const int32_t *offs, void *out, int out_kind,
-    const float *eltwise, float factor, int relu, uint32_t N, uint32_t ICb, uint32_t Hp, uint32_t Wp, uint32_t OC,
-    uint32_t OCr, uint32_t OH, uint32_t OW, uint32_t FH, uint32_t FW, uint32_t sH, uint32_t sW, uint32_t dH,
-    uint32_t dW, cudaStream_t st)
+// run the implicit-GEMM kernel (all pointers device)
+EE launch_conv_tcgen05(const ConvGeom &g, const ConvLaunch &a, cudaStream_t st)
 {
     DeviceCtx *c = ctx();
     if (c == nullptr) {
@@ -580,94 +723,139 @@ EE launch_conv_tcgen05(const uint8_t *xp, const int8_t *w, const int32_t *offs, 
     }
     ConvParams p;
     std::memset(&p, 0, sizeof(p));
+    uint32_t N = g.in.n, OH = g.out.h, OW = g.out.w, H = a.H, W = a.W;
+    const uint32_t OC = g.out.c, FH = g.f.h, FW = g.f.w;
+    const uint32_t sH = g.sH, sW = g.sW;
+    // border classes (only when padding is applied through the coordinates)
+    p.n_rc = 1;
+    p.n_cc = 1;
+    p.rc_hi[0] = (uint8_t)(FH - 1);
+    p.cc_hi[0] = (uint8_t)(FW - 1);
+    if (a.pt != 0 || a.pl != 0 || g.pb != 0 || g.pr != 0) {
+        if (a.pt != 0 || a.pl != 0 || H == g.in.h) {   // not a padded copy
+            p.n_rc = axis_classes(OH, H, FH, sH, g.dH, (uint32_t)a.pt, p.rc_lo, p.rc_hi, p.row_class);
+            p.n_cc = axis_classes(OW, W, FW, sW, g.dW, (uint32_t)a.pl, p.cc_lo, p.cc_hi, p.col_class);
+            if (p.n_rc == 0 || p.n_cc == 0 || p.n_rc * p.n_cc > (uint32_t)MAX_CLASSES) {
+                return NOT_SUPPORTED;  // the caller falls back to a padded copy
+            }
+        }
+    }
+    // 1x1, stride 1, nothing padded: every image is one row of H*W pixels
+    if (FH == 1 && FW == 1 && sH == 1 && sW == 1 && p.n_rc == 1 && p.n_cc == 1 && a.pt == 0 && a.pl == 0 && OH == H &&
+        OW == W) {
+        W = OW = H * W;
+        H = OH = 1;
+    }
     p.N = N;
     p.OH = OH;
     p.OW = OW;
     p.OC = OC;
-    // output patch of 128 pixels: the shape that wastes the fewest rows
-    // With stride 1 along W a row of TW pixels is TW*16 contiguous bytes; the (c16, w) dimensions are
-    // then merged so that TMA moves one 16*TW-byte run per row instead of TW 16-byte ones (a TMA box
-    // is at most 256 elements wide, hence TW <= 16 on that path).
+    // Tile: TW x TH pixels of TN images, at most 128 in all; the shape that needs the fewest tiles, wider rows
+    // first among equals.  With stride 1 along W a row of TW pixels is TW*16 contiguous bytes; the (c16, w)
+    // dimensions are then merged so that TMA moves one 16*TW-byte run per row instead of TW 16-byte ones (a
+    // TMA box is at most 256 elements wide, hence TW <= 16 on that path).
     const bool merged_w = (sW == 1);
-    uint32_t best_tw = 128, best_tiles = 0xFFFFFFFFu;
-    for (uint32_t tw = merged_w ? 16 : 128; tw >= 1; tw >>= 1) {
-        const uint32_t th = 128 / tw;
-        if (tw * sW > 256 || th * sH > 256) {
+    uint64_t best_tiles = ~0ull;
+    uint32_t btw = 0, bth = 0, btn = 0;
+    const uint32_t tw_max = merged_w ? 16u : 128u;
+    for (uint32_t tw = (OW < tw_max ? OW : tw_max); tw >= 1; --tw) {
+        if (tw * sW > 256) {
             continue;
         }
-        const uint32_t tiles = ((OW + tw - 1) / tw) * ((OH + th - 1) / th);
-        if (tiles < best_tiles) {
-            best_tiles = tiles;
-            best_tw = tw;
+        for (uint32_t th = (OH < 128 / tw ? OH : 128 / tw); th >= 1; --th) {
+            if (th * sH > 256) {
+                continue;
+            }
+            uint32_t tn = 128 / (tw * th);
+            tn = tn < N ? tn : N;
+            if (tn == 0) {
+                continue;
+            }
+            const uint64_t tiles = (uint64_t)((OW + tw - 1) / tw) * ((OH + th - 1) / th) * ((N + tn - 1) / tn);
+            if (tiles < best_tiles) {
+                best_tiles = tiles;
+                btw = tw;
+                bth = th;
+                btn = tn;
+            }
         }
     }
-    if (best_tiles == 0xFFFFFFFFu) {
+    if (btw == 0) {
         return NOT_SUPPORTED;
     }
-    p.TW = best_tw;
-    p.TH = 128 / best_tw;
-    p.tw_shift = 0;
-    while ((1u << p.tw_shift) < p.TW) {
-        ++p.tw_shift;
-    }
+    p.TW = btw;
+    p.TH = bth;
+    p.TN = btn;
+    p.rows = btw * bth * btn;
     p.tiles_w = (OW + p.TW - 1) / p.TW;
     p.tiles_h = (OH + p.TH - 1) / p.TH;
-    p.ICb = ICb;
+    p.tiles_n_img = (N + p.TN - 1) / p.TN;
+    p.ICb = g.ICb;
     p.FW = FW;
+    p.FH = FH;
     p.sH = sH;
     p.sW = sW;
-    p.dH = dH;
-    p.dW = dW;
+    p.dH = g.dH;
+    p.dW = g.dW;
+    p.pt = a.pt;
+    p.pl = a.pl;
     p.merged_w = merged_w ? 1 : 0;
     p.G = 8;
-    while (ICb % p.G != 0) {
+    while (g.ICb % p.G != 0) {
         p.G >>= 1;
     }
-    p.total_chunks = FH * FW * ICb;
+    p.total_chunks = FH * FW * g.ICb;
     p.num_kb = (p.total_chunks + 7) / 8;
-    p.tiles_m = N * p.tiles_w * p.tiles_h;
+    p.tiles_m = p.tiles_n_img * p.tiles_w * p.tiles_h;
     p.block_n = pick_conv_block_n(p.tiles_m, OC, c->sm_count);
     p.tiles_n = (OC + p.block_n - 1) / p.block_n;
-    p.out = out;
-    p.eltwise = eltwise;
-    p.offs = offs;
-    p.factor = factor;
-    p.relu = relu;
+    p.out = a.out;
+    p.eltwise = a.eltwise;
+    p.offsetC = a.offsetC;
+    p.tapsum = a.tapsum;
+    p.bias = a.bias;
+    p.fscale = a.fscale;
+    p.sI = a.sI;
+    p.sF = a.sF;
+    p.num = a.num;
+    p.relu = a.relu;
     p.status = c->d_status;
 
+    // x as (c16, W, H, N, ICb): a box {.., TN, G} lands as [chunk][image][row][pixel][16 B]
     CUtensorMap map_x, map_w;
+    const uint64_t img = (uint64_t)g.ICb * H * W * 16, plane = (uint64_t)H * W * 16;
     if (merged_w) {
-        const uint64_t dims[4] = {(uint64_t)Wp * 16, Hp, ICb, N};
-        const uint64_t strides[3] = {(uint64_t)Wp * 16, (uint64_t)Hp * Wp * 16, (uint64_t)ICb * Hp * Wp * 16};
-        const uint32_t box[4] = {p.TW * 16, p.TH * sH, p.G, 1};
+        const uint64_t dims[4] = {(uint64_t)W * 16, H, N, g.ICb};
+        const uint64_t strides[3] = {(uint64_t)W * 16, img, plane};
+        const uint32_t box[4] = {p.TW * 16, p.TH * sH, p.TN, p.G};
         const uint32_t es[4] = {1, sH, 1, 1};
-        if (!encode_tiled_u8(&map_x, 4, xp, dims, strides, box, es, 0)) {
+        if (!encode_tiled_u8(&map_x, 4, a.x, dims, strides, box, es, 0)) {
             return NOT_SUPPORTED;
         }
     } else {
-        const uint64_t dims[5] = {16, Wp, Hp, ICb, N};
-        const uint64_t strides[4] = {16, (uint64_t)Wp * 16, (uint64_t)Hp * Wp * 16, (uint64_t)ICb * Hp * Wp * 16};
-        const uint32_t box[5] = {16, p.TW * sW, p.TH * sH, p.G, 1};
+        const uint64_t dims[5] = {16, W, H, N, g.ICb};
+        const uint64_t strides[4] = {16, (uint64_t)W * 16, img, plane};
+        const uint32_t box[5] = {16, p.TW * sW, p.TH * sH, p.TN, p.G};
         const uint32_t es[5] = {1, sW, sH, 1, 1};
-        if (!encode_tiled_u8(&map_x, 5, xp, dims, strides, box, es, 0)) {
+        if (!encode_tiled_u8(&map_x, 5, a.x, dims, strides, box, es, 0)) {
             return NOT_SUPPORTED;
         }
     }
     {
         const uint64_t K = (uint64_t)p.total_chunks * 16;
-        const uint64_t dims[2] = {K, OCr};
+        const uint64_t dims[2] = {K, g.OCr};
         const uint64_t strides[1] = {K};
         const uint32_t box[2] = {(uint32_t)BLOCK_K, p.block_n};
         const uint32_t es[2] = {1, 1};
-        if (!encode_tiled_u8(&map_w, 2, w, dims, strides, box, es, 128)) {
+        if (!encode_tiled_u8(&map_w, 2, a.w, dims, strides, box, es, 128)) {
             return NOT_SUPPORTED;
         }
     }
     const uint64_t tiles = (uint64_t)p.tiles_m * p.tiles_n;
     const uint32_t grid = (uint32_t)(tiles < (uint64_t)c->sm_count ? tiles : (uint64_t)c->sm_count);
-    if (out_kind == 2) {
+    if (a.out_kind == 2) {
         conv_u8s8_tcgen05_kernel<2><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_x, map_w, p);
-    } else if (out_kind == 1) {
+    } else if (a.out_kind == 1) {
         conv_u8s8_tcgen05_kernel<1><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_x, map_w, p);
     } else {
         conv_u8s8_tcgen05_kernel<0><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_x, map_w, p);
@@ -677,6 +865,18 @@ EE launch_conv_tcgen05(const uint8_t *xp, const int8_t *w, const int32_t *offs, 
     return SUCCESS;
 }
 
+// bytes of the packed filter: offsetC, weights, per-tap sums
+size_t filter_weights_off(uint32_t fn)
+{
+    return 4 * (size_t)fn;
+}
+size_t filter_tapsum_off(uint32_t fn, uint32_t OCr, uint32_t K)
+{
+    return B200_ALIGN(4 * (size_t)fn + (size_t)OCr * K, 16);
+}
+
+}  // namespace
+
 // ---- entry-point bodies for the int8 branch (called from conv.cu) ----------------------------------------
 EE conv_i8_transform_filter_bytes(const TensorDesc *filterDesc, U32 *bytes)
 {
@@ -684,8 +884,13 @@ EE conv_i8_transform_filter_bytes(const TensorDesc *filterDesc, U32 *bytes)
     if (!get4d(filterDesc, &f) || bytes == nullptr) {
         return NOT_MATCH;
     }
-    // cpu/x86/convolution.cpp:141-166: ALIGN(fn,8) * ALIGN(fc,16) * fh * fw + 4*fn + 32
-    *bytes = B200_ALIGN(f.n, 8) * B200_ALIGN(f.c, 16) * f.h * f.w + 4 * f.n + 32;
+    // cpu/x86/convolution.cpp:141-166 counts ALIGN(fn,8) * ALIGN(fc,16) * fh * fw + 4*fn + 32; here the int32
+    // sums of every (output channel, tap) follow the weights (4 * fn * fh * fw more bytes)
+    const size_t b = filter_tapsum_off(f.n, B200_ALIGN(f.n, 8), B200_ALIGN(f.c, 16) * f.h * f.w) + 4 * (size_t)f.n * f.h * f.w + 32;
+    if (b > 0xFFFFFFFFull) {
+        return NOT_SUPPORTED;
+    }
+    *bytes = (U32)b;
     return SUCCESS;
 }
 
@@ -714,8 +919,9 @@ EE conv_i8_transform_filter(const TensorDesc *filterDesc, const void *filter, Te
     }
     cudaStream_t st = tls().stream;
     const uint32_t ICb = (f.c + 15) / 16, taps = f.h * f.w, OCr = B200_ALIGN(f.n, 8);
-    const size_t mat = (size_t)OCr * taps * ICb * 16;
-    const size_t total = 4 * (size_t)f.n + mat;
+    const uint32_t K = taps * ICb * 16;
+    const size_t ts_off = filter_tapsum_off(f.n, OCr, K);
+    const size_t total = ts_off + 4 * (size_t)f.n * taps;
     Stage sg;
     const int8_t *d_src = reinterpret_cast<const int8_t *>(sg.in(filter, (size_t)f.n * f.c * taps));
     if (d_src == nullptr) {
@@ -730,7 +936,8 @@ EE conv_i8_transform_filter(const TensorDesc *filterDesc, const void *filter, Te
     }
     const int warps = 8;
     pack_conv_filter_kernel<<<(OCr + warps - 1) / warps, warps * 32, 0, st>>>(d_src, f.n, f.c, taps, ICb, OCr,
-        reinterpret_cast<int8_t *>(d_dst + 4 * (size_t)f.n), reinterpret_cast<int32_t *>(d_dst));
+        reinterpret_cast<int8_t *>(d_dst + filter_weights_off(f.n)), reinterpret_cast<int32_t *>(d_dst),
+        reinterpret_cast<int32_t *>(d_dst + ts_off));
     count_launch();
     EE ret = cuda_ee(cudaGetLastError());
     if (ret == SUCCESS && !dst_dev) {
@@ -769,13 +976,18 @@ EE conv_i8_tmp_bytes(const TensorDesc *inputDesc, const TensorDesc *filterDesc, 
     }
     ConvGeom g;
     B200_EE(conv_geometry(inputDesc, filterDesc, outputDesc, cp, &g));
-    size_t b = 256;
-    if (g.needs_copy) {
+    // room for: an fp32 input quantized first, the padded channels-of-16 copy (needed for other layouts, and
+    // kept available for paddings the border classes cannot express), and the int32 / fp32 staging of a
+    // dynamically requantized u8 output
+    size_t b = 512;
+    if (g.in.dt == DT_F32) {
+        b += B200_ALIGN((size_t)g.in.n * g.in.c * g.in.h * g.in.w, 256);
+    }
+    if (g.needs_copy || g.pt || g.pb || g.pl || g.pr) {
         b += B200_ALIGN(g.xp_bytes, 256);
     }
-    b += B200_ALIGN(4 * (size_t)g.out.c, 256);
     if (g.out.dt == DT_U8_Q) {
-        b += (size_t)g.out.n * g.out.c * g.out.h * g.out.w * 4;  // int32 results before quantization
+        b += (size_t)g.out.n * g.out.c * g.out.h * g.out.w * 4;
     }
     if (b > 0xFFFFFFFFull) {
         return NOT_SUPPORTED;
@@ -785,17 +997,19 @@ EE conv_i8_tmp_bytes(const TensorDesc *inputDesc, const TensorDesc *filterDesc, 
 }
 
 EE quantize_i32_u8_device(const int32_t *d_src, uint64_t n, uint8_t *d_q, F32 *scale2);
+EE quantize_f32_u8_device(const float *d_src, uint64_t n, uint8_t *d_q, F32 *scale, int mode);
 
+// ext: NULL for Bolt's semantics; otherwise the extension of bolt_b200_convolution_ex
 EE conv_i8_run(const TensorDesc *inputDesc, void *input, void *eltwiseInput, const TensorDesc *filterDesc,
     const void *filter, const ConvolutionParamSpec *cp, void *scale, const void *bias, U32 tmpBytes, void *tmp,
-    const TensorDesc *outputDesc, void *output, const ActivationParamSpec *act)
+    const TensorDesc *outputDesc, void *output, const ActivationParamSpec *act, const bolt_b200_conv_ext *ext)
 {
     ConvGeom g;
     B200_EE(conv_geometry(inputDesc, filterDesc, outputDesc, cp, &g));
     if (input == nullptr || filter == nullptr || output == nullptr || tmp == nullptr || scale == nullptr) {
         return NULL_POINTER;
     }
-    if (g.in.dt != DT_U8_Q || g.f.dt != DT_I8 || (g.out.dt != DT_F32 && g.out.dt != DT_U8_Q)) {
+    if ((g.in.dt != DT_U8_Q && g.in.dt != DT_F32) || g.f.dt != DT_I8 || (g.out.dt != DT_F32 && g.out.dt != DT_U8_Q)) {
         return NOT_SUPPORTED;
     }
     if (g.f.df != DF_NCHWC2NxC4) {
@@ -811,14 +1025,13 @@ EE conv_i8_run(const TensorDesc *inputDesc, void *input, void *eltwiseInput, con
     if (B200_ALIGN(g.in.c, 16) != B200_ALIGN(g.f.c, 16) || g.out.c != g.f.n || (g.out.c % 8) != 0) {
         return NOT_MATCH;
     }
-    const bool relu = act != nullptr && act->mode != ACTIVATION_NULL;
-    if (act != nullptr && act->mode != ACTIVATION_NULL && act->mode != ACTIVATION_RELU) {
-        return NOT_SUPPORTED;
-    }
+    // The AVX512 kernels test two bits of the activation mode (flags = mode << 2, `and $0xC`,
+    // convolution_direct.cpp:2143-2146,2747; convolution_1x1_direct.cpp:366-369): ReLU is applied when
+    // mode & 3 is not zero, whatever the mode's name.
+    const bool relu = act != nullptr && ((unsigned)act->mode & 3u) != 0;
     const bool out_u8 = g.out.dt == DT_U8_Q;
-    if (out_u8 && eltwiseInput != nullptr) {
-        return NOT_SUPPORTED;  // the reference switches to an fp32 staging + F32->U8 quantize there
-    }
+    const float ext_out_scale = (ext != nullptr && out_u8) ? ext->output_scale : 0.f;
+    const void *ext_fscale = ext != nullptr ? ext->filter_scales : nullptr;
     U32 need = 0;
     B200_EE(conv_i8_tmp_bytes(inputDesc, filterDesc, outputDesc, cp, &need));
     if (tmpBytes < need) {
@@ -830,14 +1043,13 @@ EE conv_i8_run(const TensorDesc *inputDesc, void *input, void *eltwiseInput, con
     }
     cudaStream_t st = tls().stream;
     F32 *sc = reinterpret_cast<F32 *>(scale);
-    const float scaleO = sc[0] * sc[2];  // convolution_direct.cpp:2687
-    const float factor = 1 / scaleO;
     const size_t out_elems = (size_t)g.out.n * g.out.c * g.out.h * g.out.w;
-    const size_t in_bytes = (size_t)g.in.n * g.in.c * g.in.h * g.in.w;
-    const size_t w_bytes = 4 * (size_t)g.f.n + (size_t)g.OCr * g.K;
+    const size_t in_elems = (size_t)g.in.n * g.in.c * g.in.h * g.in.w;
+    const size_t ts_off = filter_tapsum_off(g.f.n, g.OCr, g.K);
+    const size_t w_bytes = ts_off + 4 * (size_t)g.f.n * g.taps;
 
     Stage sg;
-    const uint8_t *d_in = reinterpret_cast<const uint8_t *>(sg.in(input, in_bytes));
+    const void *d_in_any = sg.in(input, in_elems * (g.in.dt == DT_F32 ? 4 : 1));
     const char *d_w = nullptr;
     if (is_device_ptr(filter)) {
         d_w = reinterpret_cast<const char *>(filter);
@@ -853,18 +1065,61 @@ EE conv_i8_run(const TensorDesc *inputDesc, void *input, void *eltwiseInput, con
     }
     const float *d_bias = bias ? reinterpret_cast<const float *>(sg.in(bias, 4 * (size_t)g.out.c)) : nullptr;
     const float *d_elt = eltwiseInput ? reinterpret_cast<const float *>(sg.in(eltwiseInput, 4 * out_elems)) : nullptr;
+    const float *d_fscale = ext_fscale ? reinterpret_cast<const float *>(sg.in(ext_fscale, 4 * (size_t)g.out.c)) : nullptr;
     void *d_out = sg.out(output, out_elems * (out_u8 ? 1 : 4));
     // a host `tmp` cannot be used by the device: take device scratch of the same size instead
     char *d_tmp = is_device_ptr(tmp) ? reinterpret_cast<char *>(tmp) : reinterpret_cast<char *>(sg.scratch(need));
-    if (d_in == nullptr || d_w == nullptr || d_out == nullptr || d_tmp == nullptr || (bias && d_bias == nullptr) ||
-        (eltwiseInput && d_elt == nullptr)) {
+    if (d_in_any == nullptr || d_w == nullptr || d_out == nullptr || d_tmp == nullptr || (bias && d_bias == nullptr) ||
+        (eltwiseInput && d_elt == nullptr) || (ext_fscale && d_fscale == nullptr)) {
         return ALLOC_FAILED;
     }
     d_tmp = reinterpret_cast<char *>(B200_ALIGN(reinterpret_cast<uintptr_t>(d_tmp), 256));
-    const uint8_t *xp = d_in;
-    if (g.needs_copy) {
+    // an fp32 input is quantized first (convolution_direct.cpp:2679-2686); scale[0] is read and written as
+    // quantize_x86 does it
+    const uint8_t *d_in = reinterpret_cast<const uint8_t *>(d_in_any);
+    if (g.in.dt == DT_F32) {
+        uint8_t *q = reinterpret_cast<uint8_t *>(d_tmp);
+        d_tmp += B200_ALIGN(in_elems, 256);
+        B200_EE(quantize_f32_u8_device(reinterpret_cast<const float *>(d_in_any), in_elems, q, &sc[0], 0));
+        d_in = q;
+    }
+    const float scaleO = sc[0] * sc[2];  // convolution_direct.cpp:2687
+
+    ConvLaunch a;
+    std::memset(&a, 0, sizeof(a));
+    a.w = reinterpret_cast<const int8_t *>(d_w + filter_weights_off(g.f.n));
+    a.offsetC = reinterpret_cast<const int32_t *>(d_w);
+    a.tapsum = reinterpret_cast<const int32_t *>(d_w + ts_off);
+    a.bias = d_bias;
+    a.fscale = d_fscale;
+    a.eltwise = d_elt;
+    a.sI = sc[0];
+    a.sF = sc[2];
+    a.relu = relu ? 1 : 0;
+    // Output modes.  Bolt (ext == NULL): fp32, or u8 requantized with the dynamic scale 127 / max|acc| over the
+    // whole output, scale[1] written back (convolution_direct.cpp:2798-2806); with an eltwise input the u8
+    // result is the dynamic F32 -> U8_Q quantization of the fp32 result (:2693-2695).  Extension: a known
+    // output scale is applied in the epilogue; per-channel filter scales turn the dynamic u8 case into the
+    // fp32-staged one (accumulators of different channels are not comparable).
+    const bool fused_u8 = out_u8 && ext_out_scale > 0.f && d_elt == nullptr;
+    const bool f32_staged = out_u8 && !fused_u8 && (d_elt != nullptr || d_fscale != nullptr);
+    a.out_kind = fused_u8 ? 2 : ((out_u8 && !f32_staged) ? 0 : 1);
+    a.num = fused_u8 ? ext_out_scale : 1.0f;
+    char *staging = d_tmp + ((g.needs_copy || g.pt || g.pb || g.pl || g.pr) ? B200_ALIGN(g.xp_bytes, 256) : 0);
+    a.out = (out_u8 && !fused_u8) ? reinterpret_cast<void *>(staging) : d_out;
+
+    // input: in place with the padding folded into the coordinates, or through a padded copy
+    EE ret = NOT_SUPPORTED;
+    if (!g.needs_copy) {
+        a.x = d_in;
+        a.H = g.in.h;
+        a.W = g.in.w;
+        a.pt = (int32_t)g.pt;
+        a.pl = (int32_t)g.pl;
+        ret = launch_conv_tcgen05(g, a, st);
+    }
+    if (ret == NOT_SUPPORTED) {
         uint8_t *buf = reinterpret_cast<uint8_t *>(d_tmp);
-        d_tmp += B200_ALIGN(g.xp_bytes, 256);
         const size_t chunks = g.xp_bytes / 16;
         size_t blocks = (chunks + 255) / 256;
         if (blocks > (size_t)c->sm_count * 16) {
@@ -874,28 +1129,23 @@ EE conv_i8_run(const TensorDesc *inputDesc, void *input, void *eltwiseInput, con
         pad_relayout_kernel<<<(uint32_t)blocks, 256, 0, st>>>(d_in, g.in.n, g.in.c, g.in.h, g.in.w, in_block, g.ICb, g.Hp,
             g.Wp, g.pt, g.pl, buf);
         count_launch();
-        xp = buf;
+        a.x = buf;
+        a.H = g.Hp;
+        a.W = g.Wp;
+        a.pt = 0;
+        a.pl = 0;
+        ret = launch_conv_tcgen05(g, a, st);
     }
-    int32_t *d_offs = reinterpret_cast<int32_t *>(d_tmp);
-    d_tmp += B200_ALIGN(4 * (size_t)g.out.c, 256);
-    conv_bias_offset_kernel<<<(g.out.c + 255) / 256, 256, 0, st>>>(d_bias, reinterpret_cast<const int32_t *>(d_w), g.out.c,
-        scaleO, d_offs);
-    count_launch();
-    // Extension without a counterpart in the reference's convolution (it always requantizes
-    // dynamically): a positive output scale on entry fuses the requantization into the epilogue,
-    // with the arithmetic Bolt uses when an output scale is known (fully_connected.cpp:479-487 ->
-    // quantizeI32ToU8 with scales {out, scaleO}).
-    const bool fused_u8 = out_u8 && sc[1] > 0;
-    void *kernel_out = (out_u8 && !fused_u8) ? reinterpret_cast<void *>(d_tmp) : d_out;
-    B200_EE(launch_conv_tcgen05(xp, reinterpret_cast<const int8_t *>(d_w + 4 * (size_t)g.f.n), d_offs, kernel_out,
-        fused_u8 ? 2 : (out_u8 ? 0 : 1), d_elt, fused_u8 ? sc[1] / scaleO : factor, relu ? 1 : 0, g.in.n, g.ICb, g.Hp, g.Wp, g.out.c, g.OCr, g.out.h, g.out.w, g.f.h,
-        g.f.w, g.sH, g.sW, g.dH, g.dW, st));
+    B200_EE(ret);
     if (fused_u8) {
-        // sc[1] stays the caller's output scale
+        sc[1] = ext_out_scale;
+    } else if (f32_staged) {
+        F32 s = -1;
+        B200_EE(quantize_f32_u8_device(reinterpret_cast<const float *>(a.out), out_elems, reinterpret_cast<uint8_t *>(d_out), &s, 0));
+        sc[1] = s;
     } else if (out_u8) {
-        // convolution_direct.cpp:2798-2806: dynamic scale over the whole output, scale[1] = scaleO * 127/max
         F32 scales[2] = {-1, scaleO};
-        B200_EE(quantize_i32_u8_device(reinterpret_cast<const int32_t *>(kernel_out), out_elems,
+        B200_EE(quantize_i32_u8_device(reinterpret_cast<const int32_t *>(a.out), out_elems,
             reinterpret_cast<uint8_t *>(d_out), scales));
         sc[1] = scales[0];
     } else {

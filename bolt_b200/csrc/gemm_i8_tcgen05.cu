@@ -38,7 +38,10 @@ using namespace tc;
 
 constexpr int MAX_BLOCK_N = 256;
 constexpr int MAX_STAGES = 8;        // the ring is as deep as shared memory allows for the tile width
-constexpr int EPI_WARPS_FAST = 16;
+#ifndef B200_EPI_WARPS_FAST
+#define B200_EPI_WARPS_FAST 16
+#endif
+constexpr int EPI_WARPS_FAST = B200_EPI_WARPS_FAST;
 constexpr int EPI_WARPS_GENERAL = 8;
 constexpr uint32_t TMEM_COLS = 512;  // 2 accumulators x 256 columns
 constexpr uint32_t GROUP_M = 16;     // row blocks per raster group
@@ -75,6 +78,8 @@ struct Params {
     int *status;
     int vec_ok;             // rows of C are 16-byte aligned -> vector stores allowed
     uint32_t prefetch_slice;  // bytes of ep.prefetch each CTA asks for (0: none)
+    uint32_t balanced;        // 1: equal spans of 32-column units per worker (TileWalk), B loaded in 32-row boxes
+    uint32_t units_per_row;   // N / 32 (balanced mode)
 };
 
 // Raster: groups of GROUP_M row blocks, inside a group the row block runs fastest.
@@ -89,21 +94,71 @@ __device__ __forceinline__ void tile_coords(const Params &p, uint32_t tile, uint
     mb = first + (r - nb * gm);
 }
 
+// One tile of work: row block, first column, width in 32-column units (at most 8).
+struct Tile {
+    uint32_t mb, n0, units;
+};
+// The tiles of one worker (a CTA, or a CTA pair), in the order in which all its roles visit them.
+//   uniform : tiles of block_n columns, tile index = worker, worker + workers, ... in the grouped raster
+//   balanced: the (row block, 32-column unit) space is cut into contiguous spans of equal length (+-1
+//             unit), one per worker; a span is walked in tiles of at most 8 units that stay inside a row
+//             block.  Every SM then gets the same amount of work, where whole tiles would leave the last
+//             wave partly empty (for shapes whose operands stay in L2; the walk has no L2 blocking).
+struct TileWalk {
+    uint32_t cur, end, step;
+    __device__ __forceinline__ void init(const Params &p, uint32_t worker, uint32_t workers)
+    {
+        if (p.balanced) {
+            const uint64_t total = (uint64_t)p.tiles_m * p.units_per_row;
+            cur = (uint32_t)(total * worker / workers);
+            end = (uint32_t)(total * (worker + 1) / workers);
+            step = 0;
+        } else {
+            cur = worker;
+            end = p.tiles_m * p.tiles_n;
+            step = workers;
+        }
+    }
+    __device__ __forceinline__ bool next(const Params &p, Tile &t)
+    {
+        if (cur >= end) {
+            return false;
+        }
+        if (p.balanced) {
+            t.mb = cur / p.units_per_row;
+            const uint32_t u0 = cur - t.mb * p.units_per_row;
+            const uint32_t span = min(end - cur, p.units_per_row - u0);
+            const uint32_t nt = (span + 7) >> 3;
+            t.units = (span + nt - 1) / nt;
+            t.n0 = u0 * 32;
+            cur += t.units;
+        } else {
+            uint32_t nb;
+            tile_coords(p, cur, t.mb, nb);
+            t.n0 = nb * p.block_n;
+            t.units = p.block_n >> 5;
+            cur += step;
+        }
+        return true;
+    }
+};
+
 // ---- epilogue for 32 consecutive columns of one row: the common case ---------------------------
 // Full, 16-byte aligned chunk, C overwritten.  Per element: add offsetC, s32 -> f32 (vcvtdq2ps),
 // multiply (vmulps), then for u8 the rounding of vcvtps2dq + vpaddd 128 + vpmovusdb.
 //
-// 32 accumulators of one row -> 32 bytes (8 words), the common case: f + (1.5 * 2^23 + 128) has the bits
+// 32 accumulators of one row -> 32 bytes (8 words).  Per element: +offsetC, s32 -> f32 (vcvtdq2ps), * factor
+// (vmulps), then vcvtps2dq + vpaddd 128 + vpmovusdb in one biased add: f + (1.5 * 2^23 + 128) has the bits
 // 0x4B400000 + (rne(f) + 128) whenever -128 <= rne(f) <= 127 (the sum lies in [2^23, 2^24), where one ulp
 // is 1 and ties go to the even sum, i.e. to even rne(f)), so the low byte is the result; every other
-// input -- too large, too negative, NaN, infinity -- leaves other upper bits.  Returns the OR of
-// (bits ^ 0x4B400000) over the chunk: above 255 means that some element needs the exact routine.
+// input -- too large, too negative, NaN, infinity -- leaves other upper bits, which an OR over each group
+// of four detects; such a group (rare: the output scale does not fit the data) is redone with the exact
+// clamp.  Groups are checked separately on purpose: one OR chain over the whole chunk serialises it.
 template <bool ROWS>
-__device__ __forceinline__ uint32_t chunk_to_u8_quick(const int32_t *offs, const float *colf, uint32_t cl, float num, float rs,
+__device__ __forceinline__ void chunk_to_u8(const int32_t *offs, const float *colf, uint32_t cl, float num, float rs,
     const uint32_t (&r)[32], uint32_t (&w)[8])
 {
     constexpr uint32_t BIAS_BITS = 0x4B400000u;
-    uint32_t seen = 0;
 #pragma unroll
     for (int j = 0; j < 32; j += 4) {
         const int4 o = *reinterpret_cast<const int4 *>(offs + cl + j);
@@ -114,62 +169,22 @@ __device__ __forceinline__ uint32_t chunk_to_u8_quick(const int32_t *offs, const
             c4.z = __fdiv_rn(num, __fmul_rn(rs, c4.z));
             c4.w = __fdiv_rn(num, __fmul_rn(rs, c4.w));
         }
-        const uint32_t u0 = __float_as_uint(__fadd_rn(__fmul_rn(__int2float_rn((int)r[j] + o.x), c4.x), 12583040.0f));
-        const uint32_t u1 = __float_as_uint(__fadd_rn(__fmul_rn(__int2float_rn((int)r[j + 1] + o.y), c4.y), 12583040.0f));
-        const uint32_t u2 = __float_as_uint(__fadd_rn(__fmul_rn(__int2float_rn((int)r[j + 2] + o.z), c4.z), 12583040.0f));
-        const uint32_t u3 = __float_as_uint(__fadd_rn(__fmul_rn(__int2float_rn((int)r[j + 3] + o.w), c4.w), 12583040.0f));
-        seen |= (u0 ^ BIAS_BITS);
-        seen |= (u1 ^ BIAS_BITS);
-        seen |= (u2 ^ BIAS_BITS);
-        seen |= (u3 ^ BIAS_BITS);
+        const float g0 = __fmul_rn(__int2float_rn((int)r[j] + o.x), c4.x);
+        const float g1 = __fmul_rn(__int2float_rn((int)r[j + 1] + o.y), c4.y);
+        const float g2 = __fmul_rn(__int2float_rn((int)r[j + 2] + o.z), c4.z);
+        const float g3 = __fmul_rn(__int2float_rn((int)r[j + 3] + o.w), c4.w);
+        uint32_t u0 = __float_as_uint(__fadd_rn(g0, 12583040.0f));
+        uint32_t u1 = __float_as_uint(__fadd_rn(g1, 12583040.0f));
+        uint32_t u2 = __float_as_uint(__fadd_rn(g2, 12583040.0f));
+        uint32_t u3 = __float_as_uint(__fadd_rn(g3, 12583040.0f));
+        const uint32_t seen = (u0 ^ BIAS_BITS) | (u1 ^ BIAS_BITS) | (u2 ^ BIAS_BITS) | (u3 ^ BIAS_BITS);
+        if (__builtin_expect(seen > 255u, 0)) {
+            u0 = f32_to_u8_zp128(g0);
+            u1 = f32_to_u8_zp128(g1);
+            u2 = f32_to_u8_zp128(g2);
+            u3 = f32_to_u8_zp128(g3);
+        }
         w[j >> 2] = __byte_perm(__byte_perm(u0, u1, 0x0040), __byte_perm(u2, u3, 0x0040), 0x5410);
-    }
-    return seen;
-}
-// The same chunk with the exact conversion (any input).  Rare -- an element beyond the u8 range means
-// that the output scale does not fit the data -- so it is kept out of line and fetches the accumulators
-// again from tensor memory instead of keeping them alive across the common path.  Called by whole warps.
-struct Words8 {
-    uint32_t w[8];
-};
-template <bool ROWS>
-__device__ __noinline__ Words8 chunk_to_u8_exact(uint32_t taddr, const int32_t *offs, const float *colf, uint32_t cl,
-    float num, float rs)
-{
-    uint32_t r[32];
-    tmem_ld32(taddr, r);
-    tmem_ld_wait(r);
-    Words8 out;
-#pragma unroll
-    for (int j = 0; j < 32; j += 4) {
-        const int4 o = *reinterpret_cast<const int4 *>(offs + cl + j);
-        float4 c4 = *reinterpret_cast<const float4 *>(colf + cl + j);
-        if (ROWS) {
-            c4.x = __fdiv_rn(num, __fmul_rn(rs, c4.x));
-            c4.y = __fdiv_rn(num, __fmul_rn(rs, c4.y));
-            c4.z = __fdiv_rn(num, __fmul_rn(rs, c4.z));
-            c4.w = __fdiv_rn(num, __fmul_rn(rs, c4.w));
-        }
-        const uint32_t b0 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j] + o.x), c4.x));
-        const uint32_t b1 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j + 1] + o.y), c4.y));
-        const uint32_t b2 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j + 2] + o.z), c4.z));
-        const uint32_t b3 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j + 3] + o.w), c4.w));
-        out.w[j >> 2] = __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
-    }
-    return out;
-}
-// quick conversion, redone exactly for the whole warp when any lane saw an element out of range
-template <bool ROWS>
-__device__ __forceinline__ void chunk_to_u8(uint32_t taddr, const int32_t *offs, const float *colf, uint32_t cl, float num,
-    float rs, const uint32_t (&r)[32], uint32_t (&w)[8])
-{
-    const uint32_t seen = chunk_to_u8_quick<ROWS>(offs, colf, cl, num, rs, r, w);
-    if (__any_sync(0xffffffffu, seen > 255u)) {
-        const Words8 e = chunk_to_u8_exact<ROWS>(taddr, offs, colf, cl, num, rs);
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-            w[q] = e.w[q];
-        }
     }
 }
 // 32 bytes of row `lane` into the warp's staging box [32 rows][32 B], 32-byte swizzle: the 16-byte
@@ -357,10 +372,10 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     // 128-byte swizzled tiles need 1024-byte aligned bases
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *smem_a = smem;
-    const uint32_t b_rows = PAIR ? (p.block_n >> 1) : p.block_n;  // rows of the B tile this CTA holds
+    const uint32_t b_rows = PAIR ? (p.block_n >> 1) : p.block_n;  // rows of a full B tile this CTA holds
     const uint32_t b_stage = (b_rows * BLOCK_K + 1023u) & ~1023u;  // every stage stays 1024-byte aligned
     const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
-    const uint32_t cta = PAIR ? (blockIdx.x >> 1) : blockIdx.x;       // index among the tile workers
+    const uint32_t worker = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
     const uint32_t workers = PAIR ? (gridDim.x >> 1) : gridDim.x;
     uint8_t *smem_b = smem + p.stages * SMEM_A_STAGE;
     uint8_t *smem_staging = smem + SMEM_RING_BYTES;  // 1024-byte aligned
@@ -368,12 +383,6 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
-    const uint32_t num_tiles = p.tiles_m * p.tiles_n;
-    // bytes that complete on one full barrier: both CTAs' tiles in pair mode
-    const uint32_t stage_bytes = (PAIR ? 2u : 1u) * (uint32_t)(BLOCK_M + b_rows) * BLOCK_K;
-    const uint32_t nch = p.block_n >> 5;
-    const uint32_t cpg = (nch + GROUPS - 1) / GROUPS;          // 32-column chunks per column group
-    const uint32_t active_groups = (nch + cpg - 1) / cpg;
 
     if (threadIdx.x == 0) {
         prefetch_tensormap(&map_a);
@@ -387,8 +396,8 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&ctl->tmem_full[a], 1);
-            // one arrival per working epilogue warp (of both CTAs in pair mode)
-            mbar_init(&ctl->tmem_empty[a], (PAIR ? 8 : 4) * active_groups);
+            // one arrival per epilogue warp (of both CTAs in pair mode), whether or not it owns columns
+            mbar_init(&ctl->tmem_empty[a], (PAIR ? 2 : 1) * EW);
         }
         ctl->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -429,28 +438,40 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             // this CTA's slice of the memory a later kernel will read, requested once the pipeline is filled
             uint32_t issued = 0;
             const uint32_t fill = min(p.stages, p.num_kb);
-            for (uint32_t tile = cta; ok && tile < num_tiles; tile += workers) {
-                uint32_t mb, nb;
-                tile_coords(p, tile, mb, nb);
-                const int m0 = (int)((PAIR ? 2 * mb + rank : mb) * BLOCK_M);
-                const int n0 = (int)(nb * p.block_n + rank * b_rows);
+            TileWalk walk;
+            walk.init(p, worker, workers);
+            Tile t;
+            while (ok && walk.next(p, t)) {
+                const int m0 = (int)((PAIR ? 2 * t.mb + rank : t.mb) * BLOCK_M);
+                const uint32_t my_rows = PAIR ? (t.units * 16) : (t.units * 32);  // B rows this CTA loads
+                const int n0 = (int)(t.n0 + rank * my_rows);
+                const uint32_t tile_bytes = (PAIR ? 2u : 1u) * (BLOCK_M + my_rows) * BLOCK_K;
                 for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
                     if (!mbar_wait(&ctl->empty[stage], phase ^ 1)) {
                         ok = false;
                         break;
                     }
+                    uint8_t *sa = smem_a + stage * SMEM_A_STAGE;
+                    uint8_t *sb = smem_b + stage * b_stage;
                     if (PAIR) {
                         // both CTAs' bytes are expected by, and complete on, the leader's barrier
                         const uint32_t bar = mapa_shared(smem_u32(&ctl->full[stage]), 0);
                         if (rank == 0) {
-                            mbar_expect_tx(&ctl->full[stage], stage_bytes);
+                            mbar_expect_tx(&ctl->full[stage], tile_bytes);
                         }
-                        tma_load_2d_pair(&map_a, bar, smem_a + stage * SMEM_A_STAGE, (int)(kb * BLOCK_K), m0);
-                        tma_load_2d_pair(&map_b, bar, smem_b + stage * b_stage, (int)(kb * BLOCK_K), n0);
+                        tma_load_2d_pair(&map_a, bar, sa, (int)(kb * BLOCK_K), m0);
+                        tma_load_2d_pair(&map_b, bar, sb, (int)(kb * BLOCK_K), n0);
                     } else {
-                        mbar_expect_tx(&ctl->full[stage], stage_bytes);
-                        tma_load_2d(&map_a, &ctl->full[stage], smem_a + stage * SMEM_A_STAGE, (int)(kb * BLOCK_K), m0);
-                        tma_load_2d(&map_b, &ctl->full[stage], smem_b + stage * b_stage, (int)(kb * BLOCK_K), n0);
+                        mbar_expect_tx(&ctl->full[stage], tile_bytes);
+                        tma_load_2d(&map_a, &ctl->full[stage], sa, (int)(kb * BLOCK_K), m0);
+                        if (p.balanced) {
+                            // the tile width varies: B arrives in boxes of 32 rows (4 KiB each)
+                            for (uint32_t u = 0; u < t.units; ++u) {
+                                tma_load_2d(&map_b, &ctl->full[stage], sb + u * 32 * BLOCK_K, (int)(kb * BLOCK_K), n0 + (int)(u * 32));
+                            }
+                        } else {
+                            tma_load_2d(&map_b, &ctl->full[stage], sb, (int)(kb * BLOCK_K), n0);
+                        }
                     }
                     if (++stage == p.stages) {
                         stage = 0;
@@ -476,11 +497,14 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     } else if (warp == 1) {
         // ------------------------------- MMA issuer ---------------------------------------------
         if (lane == 0 && rank == 0) {
-            const uint32_t idesc = make_idesc_i8(p.block_n, PAIR ? 2 * BLOCK_M : BLOCK_M);
             uint32_t stage = 0, phase = 0;
             uint32_t it = 0;
             bool ok = true;
-            for (uint32_t tile = cta; ok && tile < num_tiles; tile += workers, ++it) {
+            TileWalk walk;
+            walk.init(p, worker, workers);
+            Tile t;
+            for (; ok && walk.next(p, t); ++it) {
+                const uint32_t idesc = make_idesc_i8(t.units * 32, PAIR ? 2 * BLOCK_M : BLOCK_M);
                 const uint32_t acc = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1;
                 if (!mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1)) {
@@ -540,8 +564,6 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         const uint32_t grp = ew >> 2;     // which share of the tile's columns
         uint8_t *stg = smem_staging + ew * STAGING_PER_WARP;
         const GemmEpilogue &ep = p.ep;
-        const uint32_t c_begin = min(nch, grp * cpg);
-        const uint32_t c_end = min(nch, c_begin + cpg);
         // Column constants (offsetC and the conversion factor): every warp keeps those of its own
         // columns in its own slice of shared memory, lane l owning columns l, l+32, ... of the warp's
         // range.  The next tile's values are fetched into registers before the current accumulator
@@ -552,15 +574,20 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         int32_t *offs = ctl->offs + ew * SLOTS;
         float *colf = ctl->colf + ew * SLOTS;
         constexpr int NQ = SLOTS / 32;
-        const uint32_t my_cols = (c_end - c_begin) * 32;
-        auto fetch_raw = [&](uint32_t tile_n0, int32_t (&o)[NQ], float (&sb)[NQ]) {
+        // this warp's 32-column chunks [c_begin, c_end) of a tile that is `units` chunks wide
+        auto my_chunks = [&](uint32_t units, uint32_t &c_begin, uint32_t &c_end) {
+            const uint32_t cpg = (units + GROUPS - 1) / GROUPS;
+            c_begin = min(units, grp * cpg);
+            c_end = min(units, c_begin + cpg);
+        };
+        auto fetch_raw = [&](uint32_t n_first, uint32_t cols, int32_t (&o)[NQ], float (&sb)[NQ]) {
 #pragma unroll
             for (int q = 0; q < NQ; ++q) {
                 o[q] = 0;
                 sb[q] = ep.sB;
                 const uint32_t j = lane + 32 * q;
-                const uint32_t n = tile_n0 + c_begin * 32 + j;
-                if (j < my_cols && n < p.N) {
+                const uint32_t n = n_first + j;
+                if (j < cols && n < p.N) {
                     if (ep.offsetC != nullptr) {
                         asm volatile("ld.global.nc.b32 %0, [%1];" : "=r"(o[q]) : "l"(ep.offsetC + n));
                     }
@@ -597,132 +624,130 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         // where this warp reports an accumulator as read: the leader's barrier
         const uint32_t empty_bar[2] = {PAIR ? mapa_shared(smem_u32(&ctl->tmem_empty[0]), 0) : smem_u32(&ctl->tmem_empty[0]),
             PAIR ? mapa_shared(smem_u32(&ctl->tmem_empty[1]), 0) : smem_u32(&ctl->tmem_empty[1])};
-        if (c_begin < c_end) {
-            if (cta < num_tiles) {
-                int32_t o[NQ];
-                float sb[NQ];
-                uint32_t mb, nb;
-                tile_coords(p, cta, mb, nb);
-                fetch_raw(nb * p.block_n, o, sb);
-                park(o, sb);
-            }
-            uint32_t it = 0;
-            uint32_t mb = 0, nb = 0, mb_next = 0, nb_next = 0;
-            if (cta < num_tiles) {
-                tile_coords(p, cta, mb_next, nb_next);
-            }
-            for (uint32_t tile = cta; tile < num_tiles; tile += workers, ++it) {
-                const uint32_t acc = it & 1;
-                const uint32_t acc_phase = (it >> 1) & 1;
-                mb = mb_next;
-                nb = nb_next;
-                const uint32_t m0 = (PAIR ? 2 * mb + rank : mb) * BLOCK_M;
-                const uint32_t n0 = nb * p.block_n;
-                if (*reinterpret_cast<volatile uint32_t *>(&ctl->abort_flag) != 0) {
-                    break;  // some role's bounded wait ran out
-                }
-                const uint32_t next_tile = tile + workers;
-                int32_t o_next[NQ];
-                float sb_next[NQ];
-                if (next_tile < num_tiles) {
-                    tile_coords(p, next_tile, mb_next, nb_next);
-                    fetch_raw(nb_next * p.block_n, o_next, sb_next);
-                }
-                const uint32_t m = m0 + quad * 32 + lane;
-                const bool row_ok = m < p.M;
-                float rs = 0.f;
-                if (ROWS && row_ok) {
-                    rs = ep.row_scale[m];
-                }
-                bool ok = mbar_wait(&ctl->tmem_full[acc], acc_phase);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) {
-                    if (lane == 0) {
-                        atomicExch(p.status, 3);
-                        atomicExch(&ctl->abort_flag, 1u);
-                    }
-                    break;
-                }
-                tcgen05_fence_after();
-                const uint32_t tbase = tmem_base + ((quad * 32u) << 16) + acc * MAX_BLOCK_N;
-                if (KIND >= 0) {
-                    // One 32-column chunk at a time (at most two per warp): the other three warps of the
-                    // scheduler cover the tensor-memory read latency, and 32 live accumulators keep the
-                    // warp within its register share.  The accumulator goes back to the MMA warp as soon
-                    // as the last chunk has been converted (the rare exact conversion reads it again).
-                    uint32_t ra[32];
-                    for (uint32_t c = c_begin; c < c_end; ++c) {
-                        const uint32_t cl = (c - c_begin) * 32;
-                        tmem_ld32(tbase + c * 32, ra);
-                        tmem_ld_wait(ra);
-                        uint32_t w[8];
-                        if (KIND >= 2) {
-                            chunk_to_u8<ROWS>(tbase + c * 32, offs, colf, cl, ep.num, rs, ra, w);
-                        }
-                        if (c + 1 == c_end) {
-                            tcgen05_fence_before();
-                            __syncwarp();
-                            if (lane == 0) {
-                                // accumulator fully read: the MMA may reuse it
-                                if (PAIR) {
-                                    mbar_arrive_cluster(empty_bar[acc]);
-                                } else {
-                                    mbar_arrive(&ctl->tmem_empty[acc]);
-                                }
-                            }
-                        }
-                        if (KIND == 3) {
-                            // the previous box must have left the staging buffer
-                            if (lane == 0) {
-                                tma_store_wait_read();
-                            }
-                            __syncwarp();
-                            stage_u8(stg, lane, w);
-                            fence_proxy_async_smem();
-                            __syncwarp();
-                            if (lane == 0) {
-                                // rows beyond M are clipped by the tensor map
-                                tma_store_2d(&map_c, stg, (int)(n0 + c * 32), (int)(m0 + quad * 32));
-                            }
-                        } else if (KIND == 2) {
-                            if (row_ok) {
-                                uint8_t *out = reinterpret_cast<uint8_t *>(p.C) + (size_t)m * p.N + n0 + c * 32;
-                                *reinterpret_cast<uint4 *>(out) = make_uint4(w[0], w[1], w[2], w[3]);
-                                *reinterpret_cast<uint4 *>(out + 16) = make_uint4(w[4], w[5], w[6], w[7]);
-                            }
-                        } else if (row_ok) {
-                            store_chunk_fast<KIND, ROWS>(p.C, p.N, offs, colf, ep.num, rs, m, n0 + c * 32, cl, ra);
-                        }
-                    }
-                } else {
-                    uint32_t ra[32];
-                    for (uint32_t c = c_begin; c < c_end; ++c) {
-                        tmem_ld32(tbase + c * 32, ra);
-                        tmem_ld_wait(ra);
-                        if (row_ok && n0 + c * 32 < p.N) {
-                            store_chunk(p, offs, colf, m, n0 + c * 32, (c - c_begin) * 32, ra);
-                        }
-                    }
-                    tcgen05_fence_before();
-                    __syncwarp();
-                    if (lane == 0) {
-                        if (PAIR) {
-                            mbar_arrive_cluster(empty_bar[acc]);
-                        } else {
-                            mbar_arrive(&ctl->tmem_empty[acc]);
-                        }
-                    }
-                }
-                if (next_tile < num_tiles) {
-                    __syncwarp();  // every lane is done reading this tile's constants
-                    park(o_next, sb_next);
-                }
-            }
-            if (KIND == 3 && lane == 0) {
-                tma_store_wait_all();  // shared memory and the output must be settled before the CTA leaves
-            }
+        auto release = [&](uint32_t acc) {
+            tcgen05_fence_before();
             __syncwarp();
+            if (lane == 0) {
+                if (PAIR) {
+                    mbar_arrive_cluster(empty_bar[acc]);
+                } else {
+                    mbar_arrive(&ctl->tmem_empty[acc]);
+                }
+            }
+        };
+        TileWalk walk;
+        walk.init(p, worker, workers);
+        Tile t, t_next;
+        bool have = walk.next(p, t);
+        if (have) {
+            int32_t o[NQ];
+            float sb[NQ];
+            uint32_t cb, ce;
+            my_chunks(t.units, cb, ce);
+            fetch_raw(t.n0 + cb * 32, (ce - cb) * 32, o, sb);
+            park(o, sb);
         }
+        for (uint32_t it = 0; have; ++it) {
+            const uint32_t acc = it & 1;
+            const uint32_t acc_phase = (it >> 1) & 1;
+            const uint32_t m0 = (PAIR ? 2 * t.mb + rank : t.mb) * BLOCK_M;
+            const uint32_t n0 = t.n0;
+            uint32_t c_begin, c_end;
+            my_chunks(t.units, c_begin, c_end);
+            if (*reinterpret_cast<volatile uint32_t *>(&ctl->abort_flag) != 0) {
+                break;  // some role's bounded wait ran out
+            }
+            const bool have_next = walk.next(p, t_next);
+            int32_t o_next[NQ];
+            float sb_next[NQ];
+            if (have_next) {
+                uint32_t cb, ce;
+                my_chunks(t_next.units, cb, ce);
+                fetch_raw(t_next.n0 + cb * 32, (ce - cb) * 32, o_next, sb_next);
+            }
+            const uint32_t m = m0 + quad * 32 + lane;
+            const bool row_ok = m < p.M;
+            float rs = 0.f;
+            if (ROWS && row_ok) {
+                rs = ep.row_scale[m];
+            }
+            bool ok = mbar_wait(&ctl->tmem_full[acc], acc_phase);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                if (lane == 0) {
+                    atomicExch(p.status, 3);
+                    atomicExch(&ctl->abort_flag, 1u);
+                }
+                break;
+            }
+            tcgen05_fence_after();
+            const uint32_t tbase = tmem_base + ((quad * 32u) << 16) + acc * MAX_BLOCK_N;
+            if (c_begin >= c_end) {
+                release(acc);  // no columns of this tile: only the hand-back
+            } else if (KIND >= 0) {
+                // One 32-column chunk at a time (at most two per warp): the other three warps of the
+                // scheduler cover the tensor-memory read latency, and 32 live accumulators keep the
+                // warp within its register share.  The accumulator goes back to the MMA warp as soon
+                // as the last chunk has been read.
+                uint32_t ra[32];
+                for (uint32_t c = c_begin; c < c_end; ++c) {
+                    const uint32_t cl = (c - c_begin) * 32;
+                    tmem_ld32(tbase + c * 32, ra);
+                    tmem_ld_wait(ra);
+                    if (c + 1 == c_end) {
+                        release(acc);  // accumulator fully read: the MMA may reuse it
+                    }
+                    uint32_t w[8];
+                    if (KIND >= 2) {
+                        chunk_to_u8<ROWS>(offs, colf, cl, ep.num, rs, ra, w);
+                    }
+                    if (KIND == 3) {
+                        // the previous box must have left the staging buffer
+                        if (lane == 0) {
+                            tma_store_wait_read();
+                        }
+                        __syncwarp();
+                        stage_u8(stg, lane, w);
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            // rows beyond M are clipped by the tensor map
+                            tma_store_2d(&map_c, stg, (int)(n0 + c * 32), (int)(m0 + quad * 32));
+                        }
+                    } else if (KIND == 2) {
+                        if (row_ok) {
+                            uint8_t *out = reinterpret_cast<uint8_t *>(p.C) + (size_t)m * p.N + n0 + c * 32;
+                            *reinterpret_cast<uint4 *>(out) = make_uint4(w[0], w[1], w[2], w[3]);
+                            *reinterpret_cast<uint4 *>(out + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+                        }
+                    } else if (row_ok) {
+                        store_chunk_fast<KIND, ROWS>(p.C, p.N, offs, colf, ep.num, rs, m, n0 + c * 32, cl, ra);
+                    }
+                }
+            } else {
+                uint32_t ra[32];
+                for (uint32_t c = c_begin; c < c_end; ++c) {
+                    tmem_ld32(tbase + c * 32, ra);
+                    tmem_ld_wait(ra);
+                    if (row_ok && n0 + c * 32 < p.N) {
+                        store_chunk(p, offs, colf, m, n0 + c * 32, (c - c_begin) * 32, ra);
+                    }
+                }
+                release(acc);
+            }
+            if (have_next) {
+                __syncwarp();  // every lane is done reading this tile's constants
+                park(o_next, sb_next);
+            }
+            t = t_next;
+            have = have_next;
+        }
+        if (KIND == 3 && lane == 0) {
+            // the staging buffer must have been read before the CTA's shared memory goes away; the
+            // stores themselves complete before the grid does
+            tma_store_wait_read();
+        }
+        __syncwarp();
     }
 
     __syncthreads();
@@ -996,6 +1021,22 @@ EE launch_gemm_tcgen05(uint32_t M, uint32_t N, uint32_t K, const uint8_t *A, con
     const uint32_t block_m = pair ? 2 * BLOCK_M : BLOCK_M;
     p.tiles_m = (M + block_m - 1) / block_m;
     p.block_n = pick_block_n(p.tiles_m, N, pair ? pairs : c->sm_count);
+    // Equal spans of columns per SM instead of whole tiles when the last wave of whole tiles would be partly
+    // empty and the operands stay in L2 (the span walk has no L2 blocking); single CTAs only.
+    p.balanced = 0;
+    p.units_per_row = N / 32;
+    if (fast && !pair && (size_t)M * K + (size_t)N * K <= ((size_t)48 << 20)) {
+        const uint64_t units = (uint64_t)p.tiles_m * p.units_per_row;
+        const uint32_t whole = p.tiles_m * ((N + p.block_n - 1) / p.block_n);
+        const uint32_t waves = (whole + c->sm_count - 1) / c->sm_count;
+        // units on the busiest SM: whole tiles against equal spans
+        const uint64_t per_sm_whole = (uint64_t)waves * (p.block_n / 32);
+        const uint64_t per_sm_even = (units + c->sm_count - 1) / c->sm_count;
+        if (units >= (uint64_t)c->sm_count && per_sm_even * 10 <= per_sm_whole * 9) {
+            p.balanced = 1;
+            p.block_n = MAX_BLOCK_N;
+        }
+    }
     const uint32_t b_rows = pair ? p.block_n / 2 : p.block_n;
     p.stages = (uint32_t)(SMEM_RING_BYTES / (SMEM_A_STAGE + B200_ALIGN((size_t)b_rows * BLOCK_K, 1024)));
     if (p.stages > (uint32_t)MAX_STAGES) {
@@ -1006,12 +1047,12 @@ EE launch_gemm_tcgen05(uint32_t M, uint32_t N, uint32_t K, const uint8_t *A, con
 
     CUtensorMap map_a, map_b;
     if (!make_map(&map_a, A, K, M, K, BLOCK_M) ||
-        !make_map(&map_b, B, K, B200_ALIGN(N, 16), Kp, b_rows)) {
+        !make_map(&map_b, B, K, B200_ALIGN(N, 16), Kp, p.balanced ? 32u : b_rows)) {
         return NOT_SUPPORTED;
     }
     const uint32_t tiles = p.tiles_m * p.tiles_n;
     const uint32_t workers = pair ? (uint32_t)pairs : (uint32_t)c->sm_count;
-    const uint32_t grid = (tiles < workers ? tiles : workers) * (pair ? 2u : 1u);
+    const uint32_t grid = p.balanced ? workers : (tiles < workers ? tiles : workers) * (pair ? 2u : 1u);
     // u8 output: 32-row x 32-byte boxes, 32-byte swizzle, stored by TMA from the epilogue's staging
     CUtensorMap map_c = map_a;  // placeholder for the kinds that never touch it
     bool tma_c = false;

@@ -350,6 +350,29 @@ EE quantize_i32_u8_device(const int32_t *d_src, uint64_t n, uint8_t *d_q, F32 *s
     return SUCCESS;
 }
 
+// F32 -> U8_Q on device pointers, scale handling of quantize_x86 (cpu/x86/quantize.cpp:33-41,
+// avx512/quantize.cpp:129-133): the dynamic scale 127 / max|x| unless mode != 0 and a positive scale is given
+EE quantize_f32_u8_device(const float *d_src, uint64_t n, uint8_t *d_q, F32 *scale, int mode)
+{
+    DeviceCtx *c = ctx();
+    if (c == nullptr) {
+        return UNKNOWN;
+    }
+    if (!mode || *scale <= 0) {
+        float mx = 0;
+        B200_EE(absmax_f32_host(d_src, n, &mx));
+        const float s = (mx == 0) ? 1.0f : 127 / mx;
+        *scale = (*scale > s) ? *scale : s;
+    }
+    if (n == 0) {
+        return SUCCESS;
+    }
+    to8_kernel<float, F32ToU8><<<grid_for((n + 15) / 16, c->sm_count), TPB, 0, tls().stream>>>(d_src, n, d_q, F32ToU8{*scale});
+    count_launch();
+    B200_CUDA(cudaGetLastError());
+    return SUCCESS;
+}
+
 }  // namespace b200
 
 using namespace b200;

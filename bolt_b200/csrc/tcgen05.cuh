@@ -15,7 +15,10 @@ constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // per wait, about 2 s; f
 // A waiting thread is suspended by the hardware until the barrier flips or this many nanoseconds pass;
 // it then polls again.  Long enough that idle warps issue next to nothing, and harmless to latency
 // (the wake-up on completion is immediate).
-constexpr uint32_t TRY_WAIT_SUSPEND_NS = 20000;
+#ifndef B200_TRY_WAIT_NS
+#define B200_TRY_WAIT_NS 20000
+#endif
+constexpr uint32_t TRY_WAIT_SUSPEND_NS = B200_TRY_WAIT_NS;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
 {

@@ -45,6 +45,7 @@ class Linear:
         self.packed = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
         matrix_matrix_multiply_transform_rhs(desc, C.c_void_p(src.data_ptr()), C.c_void_p(self.packed.data_ptr()))
         torch.cuda.current_stream().synchronize()
+        self.Wq_host = Wq  # kept for checks against a CPU computation
         self.w_scale_host = np.asarray(w_scale, np.float32)
         self.uniform = bool(np.all(self.w_scale_host == self.w_scale_host[0]))
         self.w_scale = torch.from_numpy(self.w_scale_host.copy()).cuda()

@@ -1,6 +1,6 @@
 """Synthetic workloads for the kernels next to the headline GEMM stack: the FFN-shaped GEMM sweep
-and GEMV (BASELINE config 4), the ResNet-50-shaped int8 convolutions (config 3), the 1-bit
-convolution (config 5) and stand-alone quantize / dequantize.  Each returns a dict of measured
+and GEMV, the ResNet-50-shaped int8 convolutions, the 1-bit convolution, stand-alone quantize /
+dequantize and the tensor-core issue-rate probe.  Each returns a dict of measured
 figures; `bench.py --workload NAME` prints it as one JSON line.
 
 Timing: CUDA events on the launching stream, one pair per iteration, a 256 MiB read between
@@ -87,27 +87,84 @@ def _packed_weight(K, N, seed):
     return packed, rhs
 
 
+def _ffn_parity(M, K, N, a, w_host, offs_host, sB, rs, num, c, out_u8, rows):
+    """sampled rows of the device result against exact integer accumulators and the defined epilogue
+    factor = num / (sA[m] * sB[n]) (binary32 multiply, divide), computed with numpy"""
+    A = a[rows].cpu().numpy().astype(np.float64)
+    acc = (A @ w_host).astype(np.int64) + offs_host[None, :]   # w_host: float64 copy of the s8 weight, sums exact
+    fac = (np.float32(num) / (rs[rows].cpu().numpy().astype(np.float32)[:, None] * sB[None, :])).astype(np.float32)
+    f = (acc.astype(np.int32).astype(np.float32) * fac).astype(np.float32)
+    if out_u8:
+        v = np.rint(f).astype(np.int64) + 128
+        want = np.where((v >= 0) & (v <= 255), v, 255).astype(np.uint8)
+        got = c.view(M, N)[rows].cpu().numpy()
+    else:
+        want = f
+        got = c.view(_torch().float32).view(M, N)[rows].cpu().numpy()
+    return bool(got.tobytes() == want.tobytes())
+
+
 def ffn_sweep(peaks, iters=5):
-    """u8 x s8 GEMM, K 8192, N 28672, M in {16, 128, 2048, 16384}, fused u8 output."""
+    """u8 x s8 GEMM, K 8192, N 28672, M in {16, 128, 2048, 16384}: weights s8 with one scale per output
+    channel, activations u8 with one scale per token, u8 (requantized) and fp32 outputs; a sample of rows of
+    every result is compared bit for bit with a numpy computation."""
     torch = _torch()
     L, tm = lib(), Timer()
     K, N = 8192, 28672
-    packed, rhs = _packed_weight(K, N, 1)
+    gen = torch.Generator("cuda").manual_seed(1)
+    w = torch.randint(-127, 128, (K, N), dtype=torch.int8, device="cuda", generator=gen)
+    desc = tensor2df(DT_I8, DF_NORMAL, K, N)
+    nbytes, rhs = matrix_matrix_multiply_transform_rhs_bytes(desc)
+    packed = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    matrix_matrix_multiply_transform_rhs(desc, _p(w), _p(packed))
+    torch.cuda.synchronize()
+    w_host = w.cpu().numpy().astype(np.float64)
+    del w
+    offs_host = packed[rhs: rhs + 4 * N].cpu().numpy().view(np.int32).astype(np.int64)
+    sB_host = (np.float32(127.0) / (np.float32(0.05) + np.float32(0.02) * np.abs(synth.normal(7, (N,))))).astype(np.float32)
+    sB = torch.from_numpy(sB_host).cuda()
     L.bolt_b200_set_pointer_mode(1)
     rows = []
     for M in (16, 128, 2048, 16384):
-        a = torch.randint(0, 256, (M, K), dtype=torch.uint8, device="cuda")
-        c = torch.empty(M * N, dtype=torch.uint8, device="cuda")
-        ep = GemmEpilogue()
-        ep.out_dt, ep.accumulate, ep.out_scale, ep.sA, ep.sB = DT_U8_Q, 0, 0.002, 1.0, 1.0
-        ms = tm.run(lambda: L.bolt_b200_gemm_u8s8_ex(N, M, K, _p(a), _p(packed), _p(packed, rhs), _p(c), C.byref(ep)), iters)
-        ops = 2.0 * M * N * K
-        rows.append({"M": M, "ms": ms, "tops": ops / ms / 1e9, "weight_GBps": K * N / ms / 1e6})
+        a = torch.randint(0, 256, (M, K), dtype=torch.uint8, device="cuda", generator=gen)
+        rs = (torch.rand(M, device="cuda", generator=gen) * 20 + 30).float()       # per-token activation scales
+        for out_u8 in (True, False):
+            c = torch.empty(M * N * (1 if out_u8 else 4), dtype=torch.uint8, device="cuda")
+            ep = GemmEpilogue()
+            ep.out_dt, ep.accumulate, ep.out_scale = (DT_U8_Q if out_u8 else DT_F32), 0, 40.0
+            ep.sA, ep.sB = 1.0, 1.0
+            ep.row_scale, ep.col_scale = _p(rs), _p(sB)
+            call = lambda: L.bolt_b200_gemm_u8s8_ex(N, M, K, _p(a), _p(packed), _p(packed, rhs), _p(c), C.byref(ep))
+            ms = tm.run(call, iters)
+            sample = np.unique(np.linspace(0, M - 1, 6).astype(np.int64))
+            ok = _ffn_parity(M, K, N, a, w_host, offs_host, sB_host, rs, 40.0 if out_u8 else 1.0, c, out_u8, sample)
+            ops = 2.0 * M * N * K
+            rows.append({"M": M, "out": "u8" if out_u8 else "f32", "ms": ms, "tops": ops / ms / 1e9,
+                         "weight_GBps": K * N / ms / 1e6, "parity_rows": int(len(sample)), "parity": ok,
+                         "tensor_cores": int(L.bolt_b200_last_gemm_used_tensor_cores())})
+            del c
     L.bolt_b200_set_pointer_mode(0)
-    peak = 2.0 * peaks["bf16_tflops_sustained"]
     best = max(rows, key=lambda r: r["tops"])
-    return {"workload": "ffn_gemm_sweep K=8192 N=28672", "rows": rows, "best_tops": best["tops"],
-            "frac_of_2x_bf16_sustained": best["tops"] / peak, "frac_of_nominal_4500": best["tops"] / 4500.0}
+    return {"workload": "ffn_gemm_sweep K=8192 N=28672, per-channel weight scales, per-token activation scales",
+            "rows": rows, "best_tops": best["tops"],
+            "frac_of_2x_bf16_burst": best["tops"] / (2.0 * peaks["bf16_tflops"]),
+            "frac_of_2x_bf16_sustained": best["tops"] / (2.0 * peaks["bf16_tflops_sustained"]),
+            "frac_of_nominal_4500": best["tops"] / 4500.0,
+            "roofs": "M 16, 128: the 235 MB weight stream (HBM); M >= 2048: tensor pipe under the board power limit"}
+
+
+def i8_peak(peaks):
+    """tcgen05.mma.kind::i8 issue rate with nothing else in the way: a burst (about a millisecond) and
+    a run of seconds (under the power limit)."""
+    L = lib()
+    ms, tops = C.c_float(), C.c_float()
+    out = {}
+    for name, n in (("burst", 8192), ("sustained", 24000000)):
+        CHECK_STATUS(L.bolt_b200_i8_mma_rate(n, C.byref(ms), C.byref(tops)), "i8_mma_rate")
+        out[name] = {"mma_per_sm": n, "ms": ms.value, "tops": tops.value}
+    return {"workload": "i8_peak: back-to-back tcgen05.mma.kind::i8 128x256x32, one CTA per SM, no loads", **out,
+            "nominal_dense_int8_tops": 4500.0, "two_x_bf16_burst": 2.0 * peaks["bf16_tflops"],
+            "two_x_bf16_sustained": 2.0 * peaks["bf16_tflops_sustained"]}
 
 
 def gemv(peaks, iters=20):
@@ -188,7 +245,8 @@ def resnet_conv(peaks, batch=64, iters=5, out_u8=False):
     the epilogue with a known output scale."""
     torch = _torch()
     L, tm = lib(), Timer()
-    rows, tot_ops, tot_ms = [], 0.0, 0.0
+    rows, tot_ops, tot_ms, tot_roof = [], 0.0, 0.0, 0.0
+    peak_tensor = 2.0 * peaks["bf16_tflops"]   # TOP/s: no int8 entry in the measured peaks, 2 x the bf16 burst figure
     target = DT_U8_Q if out_u8 else DT_F32
     for (ic, hw, oc, k, st, pad) in RESNET50_LAYERS:
         p = conv_param(oc, k, k, st, pad, 1, True)
@@ -205,26 +263,35 @@ def resnet_conv(peaks, batch=64, iters=5, out_u8=False):
         bias = torch.randn(oc, device="cuda") * 0.1
         tmp = torch.empty(tb, dtype=torch.uint8, device="cuda")
         out = torch.empty(batch * oc * oh * oh * (1 if out_u8 else 4), dtype=torch.uint8, device="cuda")
-        sc = [31.75, 9.5 if out_u8 else -1.0, 635.0]   # u8 output: known output scale, fused requantization
+        sc = [31.75, -1.0, 635.0]
+        known_out_scale = 9.5 if out_u8 else None      # u8 output: known output scale, fused requantization
         L.bolt_b200_set_pointer_mode(1)
 
         def call():
-            convolution(in_desc, _p(x), ftm_desc, _p(ftm), p, alg, list(sc), _p(bias), tb, _p(tmp), out_desc, _p(out), True)
+            convolution(in_desc, _p(x), ftm_desc, _p(ftm), p, alg, list(sc), _p(bias), tb, _p(tmp), out_desc, _p(out), True,
+                        None, known_out_scale)
 
         fn = call
         fn = tm.graph(call)  # neither path leaves the stream: replay as a CUDA graph (no host time inside)
         ms = tm.run(fn, iters)
         L.bolt_b200_set_pointer_mode(0)
         ops = 2.0 * batch * oc * oh * oh * ic * k * k
-        rows.append({"layer": "%dx%d %d->%d @%d s%d" % (k, k, ic, oc, hw, st), "ms": ms, "tops": ops / ms / 1e9})
+        # algorithmic bytes: input + filter + output once
+        nbytes = batch * ic * hw * hw + oc * ic * k * k + batch * oc * oh * oh * (1 if out_u8 else 4)
+        t_tensor = ops / (peak_tensor * 1e12) * 1e3
+        t_hbm = nbytes / (peaks["hbm_gbs"] * 1e9) * 1e3
+        roof_ms = max(t_tensor, t_hbm)
+        rows.append({"layer": "%dx%d %d->%d @%d s%d" % (k, k, ic, oc, hw, st), "ms": ms, "tops": ops / ms / 1e9,
+                     "GBps": nbytes / ms / 1e6, "bound": "tensor" if t_tensor >= t_hbm else "hbm",
+                     "roof_ms": roof_ms, "frac_of_roof": roof_ms / ms})
         tot_ops += ops
         tot_ms += ms
+        tot_roof += roof_ms
         del w, ftm, x, tmp, out
         torch.cuda.empty_cache()
-    peak = 2.0 * peaks["bf16_tflops"]
     return {"workload": "resnet50_int8_conv batch %d (%s out)" % (batch, "u8" if out_u8 else "fp32"), "rows": rows,
-            "total_ms": tot_ms, "tops": tot_ops / tot_ms / 1e9, "frac_of_2x_bf16": tot_ops / tot_ms / 1e9 / peak,
-            "note": "each call includes the bias/offset kernel and, for padded layers, the pad+relayout pass"}
+            "total_ms": tot_ms, "tops": tot_ops / tot_ms / 1e9, "roof_total_ms": tot_roof, "frac_of_roof": tot_roof / tot_ms,
+            "roof": "per layer max(ops / (2 x bf16_tflops), algorithmic bytes / hbm_gbs); `bound` names the binding one"}
 
 
 def bnn(peaks, batch=128, iters=5):
@@ -264,4 +331,4 @@ def resnet_conv_u8(peaks):
 
 
 WORKLOADS = {"ffn": ffn_sweep, "gemv": gemv, "quantize": quantize, "resnet_conv": resnet_conv,
-             "resnet_conv_u8": resnet_conv_u8, "bnn": bnn}
+             "resnet_conv_u8": resnet_conv_u8, "bnn": bnn, "i8_peak": i8_peak}

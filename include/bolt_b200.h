@@ -160,13 +160,18 @@ extern "C" {
 /* ============================== 1. runtime =============================================== */
 
 /* What ArchInfo.archPara points at for CUDA_B200 (the slot Bolt's Mali backend uses for its
- * handle, compute/tensor/src/convolution.cpp:181-183).  NULL means device 0 / current stream. */
+ * handle, compute/tensor/src/convolution.cpp:181-183). */
 typedef struct {
     int device;
     void *stream; /* cudaStream_t */
 } bolt_b200_para;
+/* What a dispatcher's CUDA_B200 branch calls first with ArchInfo.archPara: selects the device and stream of
+ * the calling thread's later calls.  NULL: the thread's current CUDA device and the default stream. */
+EE bolt_b200_use_para(const bolt_b200_para *para);
 
-/* Select the CUDA device used by the calling thread's later calls (default 0). */
+/* Select the CUDA device used by the calling thread's later calls.  Without it the library follows the
+ * CUDA device that is current in the calling thread (cudaGetDevice).  GEMM / GEMV calls return NOT_MATCH for
+ * a data pointer that lives on another GPU. */
 EE bolt_b200_set_device(int device);
 /* Stream used by the calling thread's later calls (default: the legacy default stream). */
 EE bolt_b200_set_stream(void *cuda_stream);
@@ -186,6 +191,12 @@ EE bolt_b200_memcpy_d2h(void *dst, const void *src, size_t bytes);
 /* A packed weight written into HOST memory by a transform call keeps a device-resident twin,
  * found again by the host address.  Drop it before the host buffer is freed or reused. */
 EE bolt_b200_release_weight(const void *host_packed);
+/* Measurement aid, no counterpart in Bolt: the rate at which the GPU retires tcgen05.mma.kind::i8 when
+ * nothing else limits it -- every SM issues mma_per_sm MMAs of 128 x 256 x 32 back to back on operands
+ * resident in shared memory (no loads, no stores).  The ceiling the int8 GEMM and convolution kernels are
+ * compared with.  Blocks until the run is over; a short run (a millisecond) gives the burst figure, one of
+ * seconds the figure under the board's power limit. */
+EE bolt_b200_i8_mma_rate(U32 mma_per_sm, F32 *milliseconds, F32 *tops);
 /* Number of kernels this library has launched in this process (all threads). */
 uint64_t bolt_b200_launch_count(void);
 /* 1 if the u8 x s8 tensor-core (tcgen05) GEMM was used by the last GEMM call of this thread. */
@@ -324,12 +335,20 @@ EE bolt_b200_quantize_f32_u8_noalloc(const F32 *data, uint64_t n, UINT8 *q, F32 
 
 /* ---- int8 and 1-bit convolution --------------------------------------------------------------- */
 
+/* replaces convolution_infer_output_size_cpu (compute/tensor/src/convolution.cpp:28-108) for 4-D tensors:
+ * oh = (ih + pad_top + pad_bottom - ((fh-1)*dilation + 1)) / stride + 1 (or the SAME round modes), fn % 8 == 0
+ * required, output format DF_NCHWC16 for a U8_Q target with fn != 8 and DF_NCHWC8 otherwise -- the rule of
+ * the AVX512 int8 build (:98-103).  Note that, as in the reference, the int8 kernels always write 16-channel
+ * blocks (plus one 8-channel tail block), also under a DF_NCHWC8 descriptor. */
+EE convolution_infer_output_size_cuda_b200(const TensorDesc *inputDesc, const TensorDesc *filterDesc,
+    const ConvolutionParamSpec *convParamSpec, TensorDesc *outputDesc, DataType targetDataType);
 /* replaces compute/tensor/src/cpu/x86/convolution.cpp:23-103 */
 EE convolution_infer_forward_algorithm_cuda_b200(const TensorDesc *inputDesc,
     const TensorDesc *filterDesc, const TensorDesc *outputDesc,
     const ConvolutionParamSpec *convParamSpec, ConvolutionPolicy policy,
     ConvolutionForwardAlgorithm *algorithm, DataType targetDataType);
-/* replaces cpu/x86/convolution.cpp:105-170 */
+/* replaces cpu/x86/convolution.cpp:105-170.  int8: the reference's count plus 4*fn*fh*fw bytes, the
+ * per-tap weight sums kept behind the packed filter (they stand in for the padded copy of the input). */
 EE convolution_transform_filter_bytes_cuda_b200(const TensorDesc *filterDesc,
     const ConvolutionParamSpec *convParamSpec, ConvolutionForwardAlgorithm algorithm, U32 *bytes);
 /* replaces cpu/x86/convolution.cpp:172-231 (-> int8/convolution_transform.cpp:18-238) and, for
@@ -342,12 +361,38 @@ EE convolution_infer_forward_tmp_bytes_cuda_b200(const TensorDesc *inputDesc,
     const TensorDesc *filterDesc, const TensorDesc *outputDesc,
     const ConvolutionParamSpec *convParamSpec, ConvolutionForwardAlgorithm algorithm, U32 *bytes);
 /* replaces cpu/x86/convolution.cpp:233-363 (convolution_x86 -> convolution_int8,
- * int8/convolution.cpp:97-150) and cpu/arm/bnn/convolution.cpp:16-72 (convolution_bnn). */
+ * int8/convolution.cpp:97-150) and cpu/arm/bnn/convolution.cpp:16-72 (convolution_bnn).
+ * int8: input U8_Q (NCHWc16 / NCHWc8 / NCHW) or F32 (quantized first, scale[0] read and written like
+ * quantize_x86); scale = {scaleI, scaleO, scaleF}; scaleO = scaleI * scaleF is written to scale[1] for an
+ * fp32 output; a U8_Q output is requantized with the dynamic scale 127 / max|acc| of the whole output and
+ * scale[1] = scaleO * that -- whatever scale[1] held on entry (convolution_direct.cpp:2687,2798-2806); with
+ * an eltwise input the U8_Q output is the dynamic quantization of the fp32 result (:2693-2695).  ReLU is
+ * applied when activation mode & 3 != 0, as the AVX512 kernels test it (:2143-2146). */
 EE convolution_cuda_b200(const TensorDesc *inputDesc, void *input, void *eltwiseInput,
     const TensorDesc *filterDesc, const void *filter, const ConvolutionParamSpec *convParamSpec,
     ConvolutionForwardAlgorithm algorithm, const TensorDesc *scaleDesc, void *scale,
     const TensorDesc *biasDesc, const void *bias, U32 tmpBytes, void *tmp,
     const TensorDesc *outputDesc, void *output, const ActivationParamSpec *activationDesc);
+
+/* Extension without a counterpart in Bolt (its convolution has one weight scale per tensor and always
+ * requantizes a u8 output dynamically, convolution_direct.cpp:2687,2798-2806): convolution_cuda_b200 with
+ *   output_scale > 0  : a U8_Q output is requantized in the epilogue with this known scale,
+ *                       u8 = usat8(rne(relu(acc) * (output_scale / scaleO) + 128)) -- the arithmetic of
+ *                       quantizeI32ToU8 with both scales given (avx512/quantize.cpp:372-414); scale[1] returns it;
+ *   filter_scales     : device or host [OC], one weight scale per output channel instead of scale[2]:
+ *                       scaleO[oc] = scaleI * filter_scales[oc] in the bias term and in the conversion factor.
+ *                       A U8_Q output without output_scale is then the dynamic quantization of the fp32 result.
+ * With ext == NULL, or output_scale <= 0 and filter_scales == NULL, this is convolution_cuda_b200. */
+typedef struct {
+    F32 output_scale;
+    const F32 *filter_scales;
+} bolt_b200_conv_ext;
+EE bolt_b200_convolution_ex(const TensorDesc *inputDesc, void *input, void *eltwiseInput,
+    const TensorDesc *filterDesc, const void *filter, const ConvolutionParamSpec *convParamSpec,
+    ConvolutionForwardAlgorithm algorithm, const TensorDesc *scaleDesc, void *scale,
+    const TensorDesc *biasDesc, const void *bias, U32 tmpBytes, void *tmp,
+    const TensorDesc *outputDesc, void *output, const ActivationParamSpec *activationDesc,
+    const bolt_b200_conv_ext *ext);
 
 /* ============================== 3. operators ================================================= */
 /* Bolt's public signatures (compute/blas_enhance/include/blas_enhance.h:21-88); arch must be

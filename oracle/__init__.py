@@ -5,6 +5,8 @@
 ``oracle.ref``    : ctypes handle on ``_ref/libbolt_ref.so`` (the reference's own x86
                     AVX512-VNNI sources compiled with ``ref_shim.cpp``) or ``None`` when
                     the library is absent or the host CPU lacks avx512_vnni.
+``oracle.ref_bnn``: ctypes handle on ``_ref/libbolt_ref_bnn.so`` (the reference's scalar 1-bit
+                    convolution compiled with ``ref_bnn_shim.cpp``) or ``None`` when absent.
 
 Only ``tests/``, ``__graft_entry__.smoke()`` and the CPU-baseline / reference legs of
 ``bench.py`` may import this package.  The product package ``bolt_b200`` never does.
@@ -26,9 +28,11 @@ def build_port():
     subprocess.check_call(["make", "-s", "-C", _HERE, "all"])
 
 
-def build_ref(bolt_root="/root/reference"):
-    """Compile the reference's own int8 sources from the mounted tree, if it is there."""
-    if not os.path.isdir(bolt_root):
+def build_ref(bolt_root=None):
+    """Compile the reference's own int8 sources (and its scalar 1-bit convolution) from a mounted
+    huawei-noah/bolt tree: `bolt_root`, else the BOLT_ROOT environment variable."""
+    bolt_root = bolt_root or os.environ.get("BOLT_ROOT")
+    if not bolt_root or not os.path.isdir(bolt_root):
         return False
     subprocess.check_call(["make", "-s", "-C", _HERE, "ref", "BOLT_ROOT=" + bolt_root])
     return True
@@ -135,8 +139,21 @@ def _load_ref():
     return lib
 
 
+def _load_ref_bnn():
+    so = os.path.join(_HERE, "_ref", "libbolt_ref_bnn.so")
+    if not os.path.exists(so):
+        return None
+    try:
+        lib = _c.CDLL(so)
+    except OSError:
+        return None
+    lib.ref_bnn_conv.argtypes = [_u32] * 13 + [_i32] + [_vp] * 5
+    return lib
+
+
 port = _load_port()
 ref = _load_ref()
+ref_bnn = _load_ref_bnn()
 
 DT_I8, DT_I32, DT_F32, DT_U8_Q = 1, 3, 6, 10
 _OUT_DT = {0: np.int32, 1: np.float32, 2: np.uint8}
@@ -229,3 +246,28 @@ def ref_gemv_row(Mx, v, scale=None, m_t=False):
     rc = ref.ref_gemv_row(N, K, int(m_t), ptr(Mx), ptr(v), ptr(y), kind, ptr(s))
     assert rc == 0
     return y[:N].copy()
+
+
+def _bnn_out_elems(shape):
+    n, ic, ih, iw, oc, fh, fw, st, pad = shape
+    return n * oc * ((ih + 2 * pad - fh) // st + 1) * ((iw + 2 * pad - fw) // st + 1)
+
+
+def port_bnn(shape, xnor, xin, wbits, scale, bias):
+    """shape (n, ic, ih, iw, oc, fh, fw, stride, pad); xin / scale / bias: binary16 bit patterns;
+    returns binary16 bit patterns, NCHWc8."""
+    n, ic, ih, iw, oc, fh, fw, st, pad = shape
+    s = BnnShape(n, ic, ih, iw, oc, fh, fw, st, st, pad, pad, pad, pad, int(xnor))
+    out = np.zeros(_bnn_out_elems(shape), np.uint16)
+    port.oracle_bnn_conv(_c.byref(s), ptr(xin), ptr(wbits), ptr(scale), ptr(bias), ptr(out), None)
+    return out
+
+
+def ref_bnn_conv(shape, xnor, xin, wbits, scale, bias):
+    """the same through the reference's own scalar code (cpu/general/convolution.cpp)"""
+    n, ic, ih, iw, oc, fh, fw, st, pad = shape
+    out = np.zeros(_bnn_out_elems(shape), np.uint16)
+    rc = ref_bnn.ref_bnn_conv(n, ic, ih, iw, oc, fh, fw, st, st, pad, pad, pad, pad, int(xnor), ptr(xin), ptr(wbits),
+                              ptr(scale), ptr(bias), ptr(out))
+    assert rc == 0
+    return out

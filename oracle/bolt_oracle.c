@@ -367,7 +367,10 @@ static size_t blocked_off(uint32_t n, uint32_t C, uint32_t H, uint32_t W, uint32
  * padding value 128 (transform_functions_int8.h:41,67-79), i.e. padded taps cancel exactly;
  * fp32 output: (float)acc * (1/scaleO), + eltwise, max(0) (:2133-2165);
  * u8 output: ReLU on int32, then quantizeI32ToU8 with a dynamic scale over the whole tensor,
- * scale[1] = scaleO * raw written back (:2798-2806). */
+ * scale[1] = scaleO * raw written back (:2798-2806); u8 output with an eltwise input: the fp32 result
+ * is staged and quantized F32 -> U8_Q with its own dynamic scale (:2693-2695,2798-2806).
+ * `relu` carries the activation mode number: the kernels apply ReLU when mode & 3 != 0
+ * (flags = mode << 2 tested with `and $0xC`, :2143-2146,2747). */
 void oracle_conv_int8(const oracle_conv_shape *s, const uint8_t *in, const int8_t *filter,
     const float *bias, const float *eltwise, void *out, float *scale, int32_t *acc32)
 {
@@ -377,6 +380,9 @@ void oracle_conv_int8(const oracle_conv_shape *s, const uint8_t *in, const int8_
     float factor = 1 / scaleO;
     size_t total = (size_t)s->n * s->oc * oh * ow;
     int32_t *acc = acc32 ? acc32 : (int32_t *)malloc(total * sizeof(int32_t));
+    const int relu = (s->relu & 3u) != 0;
+    const int staged_f32 = s->out_u8 && eltwise != NULL;
+    float *fout = staged_f32 ? (float *)malloc(total * sizeof(float)) : (float *)out;
     for (uint32_t n = 0; n < s->n; ++n) {
         for (uint32_t o = 0; o < s->oc; ++o) {
             int32_t b = 0;
@@ -406,20 +412,20 @@ void oracle_conv_int8(const oracle_conv_shape *s, const uint8_t *in, const int8_
                         }
                     }
                     size_t off = blocked_off(n, s->oc, oh, ow, s->cout_block, o, y, x);
-                    if (!s->out_u8) {
+                    if (!s->out_u8 || staged_f32) {
                         float f = (float)a * factor;
                         if (eltwise != NULL) {
                             f = f + eltwise[off];
                         }
-                        if (s->relu) {
+                        if (relu) {
                             f = (f > 0) ? f : 0.0f; /* vmaxps(f, 0) */
                         }
-                        ((float *)out)[off] = f;
+                        fout[off] = f;
                         if (acc32) {
                             acc[off] = a;
                         }
                     } else {
-                        if (s->relu && a < 0) {
+                        if (relu && a < 0) {
                             a = 0; /* vpmaxsd(acc, 0) */
                         }
                         acc[off] = a;
@@ -428,7 +434,12 @@ void oracle_conv_int8(const oracle_conv_shape *s, const uint8_t *in, const int8_
             }
         }
     }
-    if (s->out_u8) {
+    if (staged_f32) {
+        float sc = -1;
+        oracle_quantize_f32_u8(fout, total, (uint8_t *)out, &sc, 0);
+        scale[1] = sc;
+        free(fout);
+    } else if (s->out_u8) {
         float sc[2] = {-1, scaleO};
         oracle_quantize_i32_u8(acc, total, (uint8_t *)out, sc);
         scale[1] = sc[0];

@@ -275,8 +275,9 @@ RefConvPlan *ref_conv_plan(uint32_t n, uint32_t ic, uint32_t ih, uint32_t iw, ui
     pl->p.dilatedRate_t = pl->p.dilatedRate_h = pl->p.dilatedRate_w = 1;
     pl->p.convolution_type = CONVOLUTION_POINTWISE;
     pl->p.dw_activation_type = ACTIVATION_NULL;
-    pl->p.pw_activation_type = relu ? ACTIVATION_RELU : ACTIVATION_NULL;
-    pl->act.mode = relu ? ACTIVATION_RELU : ACTIVATION_NULL;
+    // `relu` is the activation mode number (0 none, 1 ReLU, others as the caller's model would carry them)
+    pl->p.pw_activation_type = (ActivationMode)relu;
+    pl->act.mode = (ActivationMode)relu;
     uint32_t oh = (ih + 2 * pad - fh) / stride + 1;
     uint32_t ow = (iw + 2 * pad - fw) / stride + 1;
     DataFormat idf = in_df == 16 ? DF_NCHWC16 : (in_df == 8 ? DF_NCHWC8 : DF_NCHW);

@@ -89,6 +89,19 @@ def conv_variants(i):
     return [(b, u, r) for b in blocks for u in (0, 1) for r in (0, 1)]
 
 
+def conv_extra_variants(i):
+    """(key, out_u8, activation mode, with eltwise) beyond conv_variants: the u8 output of a layer with a
+    residual input, and activation modes that are not ReLU (2 and 3 act as ReLU, 4 as none: the kernels
+    test mode & 3)."""
+    if i not in (1, 2, 6):
+        return []
+    return [("eltu8", 1, 1, True), ("eltu8n", 1, 0, True), ("act2", 0, 2, False), ("act3u8", 1, 3, False), ("act4", 0, 4, False)]
+
+
+def conv_eltwise(i, total):
+    return synth.normal(7300 + i, (total,), 0.5)
+
+
 GEMV_ROW_SHAPES = [(1, 1), (3, 5), (4, 16), (7, 33), (17, 64), (33, 130), (64, 256), (67, 1000)]
 
 
@@ -98,3 +111,38 @@ def gemv_row_inputs(i, m_t):
     Mx = synth.u8(seed, (k, n) if m_t else (n, k))
     v = synth.s8(seed + 500, (k,))
     return Mx, v
+
+
+# 1-bit convolution: (n, ic, ih, iw, oc, fh, fw, stride, pad).  The reference's scalar branch
+# accumulates in binary16, which is exact while every partial sum stays within +-2048; with random
+# signs the partial sums of these shapes stay far below that (K = ic * fh * fw <= 2304).
+BNN_SHAPES = [(1, 8, 5, 5, 8, 3, 3, 1, 1), (2, 32, 7, 6, 32, 3, 3, 1, 1), (1, 64, 9, 9, 72, 3, 3, 2, 1),
+              (2, 40, 6, 6, 16, 1, 1, 1, 0), (1, 96, 8, 8, 48, 5, 5, 1, 2), (1, 256, 10, 10, 32, 3, 3, 1, 1)]
+
+
+def pack_bits_msb(bits):
+    """flat 0/1 array -> bytes, MSB first (the DT_BIN01 / DT_BIN11 storage, data_type.h:463-485)"""
+    return np.packbits(bits.astype(np.uint8), bitorder="big")
+
+
+def bnn_inputs(i, xnor, scaling):
+    """scaling 0: scale 1, bias 0 (the raw tap sums); 1: scales that are powers of two and biases that
+    are multiples of 1/4 (every step exact in binary16); 2: scale = mean |W| per channel and a normal
+    bias (XNOR-Net's alpha / beta).  All as binary16 bit patterns; input in NCHWc8."""
+    n, ic, ih, iw, oc, fh, fw, st, pad = BNN_SHAPES[i]
+    seed = 11000 + 10 * i + (5 if xnor else 0)
+    x = synth.normal(seed, (n, ic, ih, iw)).astype(np.float16)
+    if not xnor:
+        x = (x * np.float16(0.5) + np.float16(0.5)).astype(np.float16)   # DoReFa activations around 0.5
+    x.reshape(-1)[::7] = np.float16(0.0 if xnor else 0.5)                # values exactly on the threshold
+    wf = synth.normal(seed + 1, (oc, ic, fh, fw))
+    wbits = pack_bits_msb((wf >= 0).reshape(-1))
+    if scaling == 0:
+        scale, bias = np.ones(oc, np.float16), np.zeros(oc, np.float16)
+    elif scaling == 1:
+        scale = (2.0 ** -(np.arange(oc) % 4)).astype(np.float16)
+        bias = ((np.arange(oc) % 9 - 4) * 0.25).astype(np.float16)
+    else:
+        scale = np.abs(wf).reshape(oc, -1).mean(axis=1).astype(np.float16)
+        bias = synth.normal(seed + 2, (oc,), 0.1).astype(np.float16)
+    return to_blocked(x.view(np.uint16), 8), wbits, scale.view(np.uint16), bias.view(np.uint16)

@@ -1,5 +1,5 @@
-"""Generates tests/golden/*.npz from the UNMODIFIED reference (oracle/_ref/libbolt_ref.so, built
-from the Bolt sources by `make -C oracle ref`).  Run in a container that has the reference tree
+"""Generates tests/golden/*.npz from the UNMODIFIED reference (oracle/_ref/libbolt_ref.so and
+oracle/_ref/libbolt_ref_bnn.so, built from the Bolt sources by `make -C oracle ref BOLT_ROOT=...`).  Run in a container that has the reference tree
 and an avx512_vnni CPU:
 
     python tests/golden/make_golden.py
@@ -23,6 +23,7 @@ import oracle as O  # noqa: E402
 from oracle import ptr  # noqa: E402
 
 assert O.ref is not None, "needs oracle/_ref/libbolt_ref.so and an avx512_vnni host"
+assert O.ref_bnn is not None, "needs oracle/_ref/libbolt_ref_bnn.so (make -C oracle ref BOLT_ROOT=...)"
 
 
 def gemm_outputs():
@@ -103,6 +104,18 @@ def conv_outputs():
             O.ref.ref_conv_free(pl)
             key = "c%d_%d%d%d" % (i, blk, out_u8, relu)
             out[key], out[key + "_scale"] = res[:tot].copy(), sc.copy()
+        # u8 output with a residual input (fp32 staging + F32 -> U8_Q), and activation modes other than ReLU
+        for key, out_u8, act, with_elt in cases.conv_extra_variants(i):
+            xin, w, bias = cases.conv_inputs(i, 16 if ic % 16 == 0 else 8)
+            blk = 16 if ic % 16 == 0 else 8
+            elt = cases.conv_eltwise(i, tot) if with_elt else None
+            pl = O.ref.ref_conv_plan(n, ic, ih, iw, oc, fh, fw, st, pad, blk, 16, out_u8, act, ptr(w))
+            assert pl
+            res = np.zeros(tot + 64, np.uint8 if out_u8 else np.float32)
+            sc = np.array(cases.CONV_SCALES, np.float32)
+            assert O.ref.ref_conv_run(pl, ptr(xin.copy()), ptr(elt), ptr(bias), ptr(res), ptr(sc)) == 0
+            O.ref.ref_conv_free(pl)
+            out["c%d_%s" % (i, key)], out["c%d_%s_scale" % (i, key)] = res[:tot].copy(), sc.copy()
     return out
 
 
@@ -118,7 +131,19 @@ def gemv_row_outputs():
     return out
 
 
+def bnn_outputs():
+    """the reference's scalar 1-bit convolution (cpu/general/convolution.cpp:141-179,264-285), both modes"""
+    out = {}
+    for i, shape in enumerate(cases.BNN_SHAPES):
+        for xnor in (0, 1):
+            for scaling in (0, 1, 2):
+                xin, wbits, scale, bias = cases.bnn_inputs(i, xnor, scaling)
+                out["b%d_%d%d" % (i, xnor, scaling)] = O.ref_bnn_conv(shape, xnor, xin, wbits, scale, bias)
+    return out
+
+
 def main():
+    np.savez_compressed(os.path.join(HERE, "bnn.npz"), **bnn_outputs())
     np.savez_compressed(os.path.join(HERE, "gemv_row.npz"), **gemv_row_outputs())
     np.savez_compressed(os.path.join(HERE, "conv.npz"), **conv_outputs())
     np.savez_compressed(os.path.join(HERE, "gemm.npz"), **gemm_outputs())

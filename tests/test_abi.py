@@ -72,3 +72,43 @@ def test_wrong_arch_and_type_are_refused():
     buf = C.create_string_buffer(256)
     p = C.cast(buf, C.c_void_p)
     assert lib.b200_matrix_matrix_multiply(a, p, b, p, 64, p, bad, p, None, B.CUDA_B200) == B.NOT_MATCH
+
+
+def test_convolution_geometry_is_checked_before_any_launch():
+    """An output descriptor that does not follow from input, filter, stride and padding is refused with
+    NOT_MATCH by the byte-count entry points (host arithmetic only), for the int8 and the 1-bit path."""
+    lib = B.load()
+    n = C.c_uint32()
+    p = B.conv_param(16, 3, 3, 1, 1)
+    x = B.tensor4df(B.DT_U8_Q, B.DF_NCHWC16, 2, 16, 8, 8)
+    f = B.tensor4df(B.DT_I8, B.DF_NCHWC2NxC4, 16, 16, 3, 3)
+    good = B.tensor4df(B.DT_F32, B.DF_NCHWC8, 2, 16, 8, 8)
+    assert lib.convolution_infer_forward_tmp_bytes_cuda_b200(C.byref(x), C.byref(f), C.byref(good), C.byref(p), 1, C.byref(n)) == B.SUCCESS
+    for bad in (B.tensor4df(B.DT_F32, B.DF_NCHWC8, 2, 16, 9, 8), B.tensor4df(B.DT_F32, B.DF_NCHWC8, 2, 16, 8, 12),
+                B.tensor4df(B.DT_F32, B.DF_NCHWC8, 3, 16, 8, 8)):
+        assert lib.convolution_infer_forward_tmp_bytes_cuda_b200(C.byref(x), C.byref(f), C.byref(bad), C.byref(p), 1, C.byref(n)) == B.NOT_MATCH
+    xb = B.tensor4df(B.DT_F16, B.DF_NCHWC8, 2, 32, 8, 8)
+    fb = B.tensor4df(B.DT_BIN11, B.DF_NCHWN16C8, 16, 32, 3, 3)
+    pb = B.conv_param(16, 3, 3, 1, 1)
+    ok = B.tensor4df(B.DT_F16, B.DF_NCHWC8, 2, 16, 8, 8)
+    assert lib.convolution_infer_forward_tmp_bytes_cuda_b200(C.byref(xb), C.byref(fb), C.byref(ok), C.byref(pb), 6, C.byref(n)) == B.SUCCESS
+    for bad in (B.tensor4df(B.DT_F16, B.DF_NCHWC8, 2, 16, 10, 8), B.tensor4df(B.DT_F16, B.DF_NCHWC8, 1, 16, 8, 8)):
+        assert lib.convolution_infer_forward_tmp_bytes_cuda_b200(C.byref(xb), C.byref(fb), C.byref(bad), C.byref(pb), 6, C.byref(n)) == B.NOT_MATCH
+
+
+def test_infer_output_size_rule():
+    """convolution.cpp:28-108"""
+    x = B.tensor4df(B.DT_U8_Q, B.DF_NCHWC16, 2, 64, 56, 56)
+    f = B.tensor4df(B.DT_I8, B.DF_NCHW, 128, 64, 3, 3)
+    o = B.convolution_infer_output_size(x, f, B.conv_param(128, 3, 3, 2, 1), B.DT_U8_Q)
+    assert list(o.dims[:4]) == [28, 28, 128, 2] and o.df == B.DF_NCHWC16 and o.dt == B.DT_U8_Q
+    o = B.convolution_infer_output_size(x, f, B.conv_param(128, 3, 3, 1, 0, 2), B.DT_F32)
+    assert list(o.dims[:4]) == [52, 52, 128, 2] and o.df == B.DF_NCHWC8
+    f8 = B.tensor4df(B.DT_I8, B.DF_NCHW, 8, 64, 1, 1)
+    assert B.convolution_infer_output_size(x, f8, B.conv_param(8, 1, 1), B.DT_U8_Q).df == B.DF_NCHWC8
+    f12 = B.tensor4df(B.DT_I8, B.DF_NCHW, 12, 64, 1, 1)
+    try:
+        B.convolution_infer_output_size(x, f12, B.conv_param(12, 1, 1), B.DT_U8_Q)
+        assert False
+    except B.BoltError as e:
+        assert e.code == B.NOT_SUPPORTED

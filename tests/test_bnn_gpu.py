@@ -1,7 +1,8 @@
-"""GPU parity of the 1-bit convolution (XNOR-Net / DoReFa) through the C ABI against the scalar
-restatement of Bolt's ARMv8.2 semantics (oracle_bnn_conv).  The reference has no x86 build of this
-path (compute/tensor/tests/test_convolution_bnn.cpp:173-180 compiles to an empty main without
-_USE_FP16), so the oracle itself is anchored by hand-checkable cases in test_oracle_pins.py."""
+"""GPU parity of the 1-bit convolution (XNOR-Net / DoReFa) through the C ABI: against fixtures made by
+the reference's own scalar code (compute/tensor/src/cpu/general/convolution.cpp:141-179,264-285,
+compiled by oracle/ref_bnn_shim.cpp; tests/golden/bnn.npz), and on larger shapes against the scalar
+restatement of Bolt's ARMv8.2 kernels (oracle_bnn_conv), which test_oracle_pins.py checks against the
+same fixtures and against the compiled reference."""
 import ctypes as C
 import os
 import sys
@@ -20,9 +21,7 @@ from util import dev_zeros, dptr, hptr, to_dev, to_host  # noqa: E402
 pytestmark = pytest.mark.gpu
 
 
-def pack_bits_msb(bits):
-    """flat 0/1 array -> bytes, MSB first (the DT_BIN01 / DT_BIN11 storage, data_type.h:463-485)"""
-    return np.packbits(bits.astype(np.uint8), bitorder="big")
+pack_bits_msb = cases.pack_bits_msb
 
 
 def bnn_case(seed, n, ic, ih, iw, oc, fh, fw, st, pad, xnor):
@@ -77,6 +76,16 @@ SHAPES = [(1, 8, 5, 5, 8, 3, 3, 1, 1), (2, 32, 7, 6, 32, 3, 3, 1, 1), (1, 64, 9,
           (1, 256, 14, 14, 64, 3, 3, 1, 1), (2, 96, 8, 8, 48, 5, 5, 1, 2)]
 
 
+@pytest.mark.parametrize("i", range(len(cases.BNN_SHAPES)))
+def test_bnn_vs_reference_fixtures(i):
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "bnn.npz"))
+    shape = cases.BNN_SHAPES[i]
+    for xnor in (0, 1):
+        for scaling in (0, 1, 2):
+            got = bnn_gpu(*shape, bool(xnor), *cases.bnn_inputs(i, xnor, scaling))
+            assert got.tobytes() == g["b%d_%d%d" % (i, xnor, scaling)].tobytes(), (i, xnor, scaling)
+
+
 @pytest.mark.parametrize("xnor", [True, False])
 @pytest.mark.parametrize("shape", SHAPES)
 def test_bnn_vs_oracle(shape, xnor):
@@ -87,7 +96,7 @@ def test_bnn_vs_oracle(shape, xnor):
 
 
 def test_bnn_config5_slice_and_host_pointers():
-    """BASELINE config 5 geometry (C 256 -> 256, 28 x 28, 3 x 3, pad 1) at batch 2, both modes."""
+    """The benchmarked geometry (C 256 -> 256, 28 x 28, 3 x 3, pad 1) at batch 2, both modes."""
     shape = (2, 256, 28, 28, 256, 3, 3, 1, 1)
     for xnor in (True, False):
         data = bnn_case(5, *shape, xnor)

@@ -112,11 +112,49 @@ def test_golden_conv():
             sc = np.array(cases.CONV_SCALES, np.float32)
             O.port.oracle_conv_int8(C.byref(s), ptr(xin), ptr(w), ptr(bias), None, ptr(out), ptr(sc), None)
             assert same_bits(out, g[key]) and same_bits(sc, g[key + "_scale"]), key
+        for key, out_u8, act, with_elt in cases.conv_extra_variants(i):
+            blk = 16 if ic % 16 == 0 else 8
+            xin, w, bias = cases.conv_inputs(i, blk)
+            key = "c%d_%s" % (i, key)
+            elt = cases.conv_eltwise(i, g[key].size) if with_elt else None
+            s = O.ConvShape(n, ic, ih, iw, oc, fh, fw, st, st, pad, pad, pad, pad, 1, 1, blk, 16, act, out_u8)
+            out = np.zeros(g[key].size, g[key].dtype)
+            sc = np.array(cases.CONV_SCALES, np.float32)
+            O.port.oracle_conv_int8(C.byref(s), ptr(xin), ptr(w), ptr(bias), ptr(elt), ptr(out), ptr(sc), None)
+            assert same_bits(out, g[key]) and same_bits(sc, g[key + "_scale"]), key
+
+
+def test_golden_bnn():
+    """The restatement of the 1-bit convolution against outputs of the reference's own scalar code
+    (cpu/general/convolution.cpp:141-179,264-285, compiled by oracle/ref_bnn_shim.cpp): thresholds,
+    bit order, padding values, tap sums, scale * sum + bias -- both modes, three kinds of scale / bias."""
+    g = np.load(os.path.join(GOLD, "bnn.npz"))
+    for i, shape in enumerate(cases.BNN_SHAPES):
+        for xnor in (0, 1):
+            for scaling in (0, 1, 2):
+                got = O.port_bnn(shape, xnor, *cases.bnn_inputs(i, xnor, scaling))
+                assert same_bits(got, g["b%d_%d%d" % (i, xnor, scaling)]), (i, xnor, scaling)
+
+
+@pytest.mark.skipif(O.ref_bnn is None, reason="oracle/_ref/libbolt_ref_bnn.so not built")
+def test_ref_bnn_sweep():
+    """wider than the fixtures: odd sizes, strides, asymmetric images, against the compiled reference"""
+    k = 0
+    for n, ic, hw, oc, f, st, pad in [(1, 8, 4, 8, 1, 1, 0), (2, 16, 5, 8, 3, 2, 1), (1, 24, 7, 16, 3, 1, 0), (1, 48, 6, 24, 5, 2, 2),
+                                      (3, 8, 9, 40, 3, 3, 1), (1, 128, 5, 8, 3, 1, 1)]:
+        shape = (n, ic, hw, hw + 1, oc, f, f, st, pad)
+        for xnor in (0, 1):
+            x = synth.normal(12000 + k, (n, ic, hw, hw + 1)).astype(np.float16)
+            wbits = cases.pack_bits_msb(synth.normal(12500 + k, (oc * ic * f * f,)) >= 0)
+            scale = (synth.normal(12600 + k, (oc,)) * 0.3).astype(np.float16).view(np.uint16)
+            bias = synth.normal(12700 + k, (oc,)).astype(np.float16).view(np.uint16)
+            xin = cases.to_blocked(x.view(np.uint16), 8)
+            assert same_bits(O.port_bnn(shape, xnor, xin, wbits, scale, bias), O.ref_bnn_conv(shape, xnor, xin, wbits, scale, bias)), shape
+            k += 1
 
 
 def test_bnn_oracle_hand_checkable_cases():
-    """The 1-bit path has no runnable reference here ("parity unpinned"): anchor the restatement on
-    cases whose answers follow directly from the definitions in
+    """Cases whose answers follow directly from the definitions in
     cpu/arm/bnn/convolution_xnor_A76.cpp:67-79,300-374 and convolution_dorefa_A76.cpp:167-199."""
     import ctypes as C
     f16 = lambda v: int(np.float16(v).view(np.uint16))
