@@ -185,6 +185,9 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t num_tiles = p.tiles_m * p.tiles_n;
     const uint32_t chunk_bytes = p.rows * 16;   // one 16-byte K chunk of all the tile's pixels
+    // distance between K chunks in shared memory: TMA destinations are 128-byte aligned, so a tile whose pixel
+    // count is not a multiple of 8 gets one load per chunk (G = 1) at a rounded-up distance
+    const uint32_t chunk_stride = ((p.rows + 7u) & ~7u) * 16;
 
     if (threadIdx.x == 0) {
         prefetch_tensormap(&map_x);
@@ -245,7 +248,7 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                         const uint32_t tap = q / p.ICb;
                         const uint32_t cb = q - tap * p.ICb;
                         const uint32_t kh = tap / p.FW, kw = tap - kh * p.FW;
-                        uint8_t *dst = smem_a + stage * SMEM_A_STAGE + j * chunk_bytes;
+                        uint8_t *dst = smem_a + stage * SMEM_A_STAGE + j * chunk_stride;
                         // taps outside the image start at negative or too large coordinates and read zeros
                         const int x = (int)(ow0 * p.sW + kw * p.dW) - p.pl;
                         const int y = (int)(oh0 * p.sH + kh * p.dH) - p.pt;
@@ -295,10 +298,10 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                     const uint32_t a_addr = smem_u32(smem_a + stage * SMEM_A_STAGE);
                     const uint64_t db = make_desc_sw128(smem_u32(smem_b + stage * SMEM_B_STAGE));
                     for (uint32_t k = 0; 2 * k < nq; ++k) {
-                        // A: two 16-byte K chunks per MMA, chunk_bytes apart; 8-pixel groups 128 B apart.  Rows
+                        // A: two 16-byte K chunks per MMA, chunk_stride apart; 8-pixel groups 128 B apart.  Rows
                         // beyond the tile's pixels read the next chunk's bytes: their accumulators are never
                         // stored.  An odd last chunk pairs with stale bytes, which meet zero weights.
-                        const uint64_t da = make_desc_noswizzle(a_addr + k * 2 * chunk_bytes, chunk_bytes, 128);
+                        const uint64_t da = make_desc_noswizzle(a_addr + k * 2 * chunk_stride, chunk_stride, 128);
                         umma_i8(tmem_d, da, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
                     }
                     tcgen05_commit(&ctl->empty[stage]);
@@ -803,6 +806,9 @@ EE launch_conv_tcgen05(const ConvGeom &g, const ConvLaunch &a, cudaStream_t st)
     p.G = 8;
     while (g.ICb % p.G != 0) {
         p.G >>= 1;
+    }
+    if (p.rows % 8 != 0) {
+        p.G = 1;  // chunks of a box follow each other without gaps; only whole 128-byte units may be merged
     }
     p.total_chunks = FH * FW * g.ICb;
     p.num_kb = (p.total_chunks + 7) / 8;

@@ -78,8 +78,6 @@ struct Params {
     int *status;
     int vec_ok;             // rows of C are 16-byte aligned -> vector stores allowed
     uint32_t prefetch_slice;  // bytes of ep.prefetch each CTA asks for (0: none)
-    uint32_t balanced;        // 1: equal spans of 32-column units per worker (TileWalk), B loaded in 32-row boxes
-    uint32_t units_per_row;   // N / 32 (balanced mode)
 };
 
 // Raster: groups of GROUP_M row blocks, inside a group the row block runs fastest.
@@ -98,47 +96,48 @@ __device__ __forceinline__ void tile_coords(const Params &p, uint32_t tile, uint
 struct Tile {
     uint32_t mb, n0, units;
 };
-// The tiles of one worker (a CTA, or a CTA pair), in the order in which all its roles visit them.
-//   uniform : tiles of block_n columns, tile index = worker, worker + workers, ... in the grouped raster
-//   balanced: the (row block, 32-column unit) space is cut into contiguous spans of equal length (+-1
-//             unit), one per worker; a span is walked in tiles of at most 8 units that stay inside a row
-//             block.  Every SM then gets the same amount of work, where whole tiles would leave the last
-//             wave partly empty (for shapes whose operands stay in L2; the walk has no L2 blocking).
+// The tiles of one worker (a CTA, or a CTA pair), in the order in which all its roles visit them: tile
+// index = worker, worker + workers, ... in the grouped raster.
+// (Cutting the columns into equal spans per SM instead of whole tiles -- no partly empty last wave -- was
+// measured slower on the 4096 x 3072 x 768 shape: 13.5 us against 11.7 us per launch.)
 struct TileWalk {
     uint32_t cur, end, step;
+    uint32_t first, r;   // first row block of the current raster group, position inside the group
     __device__ __forceinline__ void init(const Params &p, uint32_t worker, uint32_t workers)
     {
-        if (p.balanced) {
-            const uint64_t total = (uint64_t)p.tiles_m * p.units_per_row;
-            cur = (uint32_t)(total * worker / workers);
-            end = (uint32_t)(total * (worker + 1) / workers);
-            step = 0;
-        } else {
-            cur = worker;
-            end = p.tiles_m * p.tiles_n;
-            step = workers;
-        }
+        cur = worker;
+        end = p.tiles_m * p.tiles_n;
+        step = workers;
+        const uint32_t per_group = GROUP_M * p.tiles_n;
+        const uint32_t g = worker / per_group;
+        first = g * GROUP_M;
+        r = worker - g * per_group;
     }
+    // every role of a CTA calls this once per tile; after the first call it costs no division (the roles
+    // of a warp wait on one another through it, so it sits on the epilogue's critical path)
     __device__ __forceinline__ bool next(const Params &p, Tile &t)
     {
         if (cur >= end) {
             return false;
         }
-        if (p.balanced) {
-            t.mb = cur / p.units_per_row;
-            const uint32_t u0 = cur - t.mb * p.units_per_row;
-            const uint32_t span = min(end - cur, p.units_per_row - u0);
-            const uint32_t nt = (span + 7) >> 3;
-            t.units = (span + nt - 1) / nt;
-            t.n0 = u0 * 32;
-            cur += t.units;
-        } else {
-            uint32_t nb;
-            tile_coords(p, cur, t.mb, nb);
-            t.n0 = nb * p.block_n;
-            t.units = p.block_n >> 5;
-            cur += step;
+        uint32_t gm = min(GROUP_M, p.tiles_m - first);
+        while (r >= gm * p.tiles_n) {   // into the next raster group(s)
+            r -= gm * p.tiles_n;
+            first += gm;
+            gm = min(GROUP_M, p.tiles_m - first);
         }
+        uint32_t nb;
+        if (gm == GROUP_M) {
+            nb = r / GROUP_M;           // a shift
+            t.mb = first + (r & (GROUP_M - 1));
+        } else {
+            nb = r / gm;
+            t.mb = first + (r - nb * gm);
+        }
+        t.n0 = nb * p.block_n;
+        t.units = p.block_n >> 5;
+        cur += step;
+        r += step;
         return true;
     }
 };
@@ -151,14 +150,60 @@ struct TileWalk {
 // (vmulps), then vcvtps2dq + vpaddd 128 + vpmovusdb in one biased add: f + (1.5 * 2^23 + 128) has the bits
 // 0x4B400000 + (rne(f) + 128) whenever -128 <= rne(f) <= 127 (the sum lies in [2^23, 2^24), where one ulp
 // is 1 and ties go to the even sum, i.e. to even rne(f)), so the low byte is the result; every other
-// input -- too large, too negative, NaN, infinity -- leaves other upper bits, which an OR over each group
-// of four detects; such a group (rare: the output scale does not fit the data) is redone with the exact
-// clamp.  Groups are checked separately on purpose: one OR chain over the whole chunk serialises it.
+// input -- too large, too negative, NaN, infinity -- leaves other upper bits.  Returns the OR of
+// (bits ^ 0x4B400000) over the chunk: above 255 means that some element needs the exact clamp.
+// Written stage by stage over the whole chunk, in place and without a branch, so that the 32 elements
+// overlap: an epilogue warp works through its tiles one after the other and the latency of this routine
+// is what paces the kernel when K is short.
 template <bool ROWS>
-__device__ __forceinline__ void chunk_to_u8(const int32_t *offs, const float *colf, uint32_t cl, float num, float rs,
-    const uint32_t (&r)[32], uint32_t (&w)[8])
+__device__ __forceinline__ uint32_t chunk_to_u8_quick(const int32_t *offs, const float *colf, uint32_t cl, float num, float rs,
+    uint32_t (&r)[32], uint32_t (&w)[8])
 {
     constexpr uint32_t BIAS_BITS = 0x4B400000u;
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+        const int4 o = *reinterpret_cast<const int4 *>(offs + cl + j);
+        r[j] += (uint32_t)o.x;
+        r[j + 1] += (uint32_t)o.y;
+        r[j + 2] += (uint32_t)o.z;
+        r[j + 3] += (uint32_t)o.w;
+    }
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+        float4 c4 = *reinterpret_cast<const float4 *>(colf + cl + j);
+        if (ROWS) {
+            c4.x = __fdiv_rn(num, __fmul_rn(rs, c4.x));
+            c4.y = __fdiv_rn(num, __fmul_rn(rs, c4.y));
+            c4.z = __fdiv_rn(num, __fmul_rn(rs, c4.z));
+            c4.w = __fdiv_rn(num, __fmul_rn(rs, c4.w));
+        }
+        r[j] = __float_as_uint(__fadd_rn(__fmul_rn(__int2float_rn((int)r[j]), c4.x), 12583040.0f));
+        r[j + 1] = __float_as_uint(__fadd_rn(__fmul_rn(__int2float_rn((int)r[j + 1]), c4.y), 12583040.0f));
+        r[j + 2] = __float_as_uint(__fadd_rn(__fmul_rn(__int2float_rn((int)r[j + 2]), c4.z), 12583040.0f));
+        r[j + 3] = __float_as_uint(__fadd_rn(__fmul_rn(__int2float_rn((int)r[j + 3]), c4.w), 12583040.0f));
+    }
+    uint32_t s8[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+        s8[q] = (r[4 * q] ^ BIAS_BITS) | (r[4 * q + 1] ^ BIAS_BITS) | (r[4 * q + 2] ^ BIAS_BITS) | (r[4 * q + 3] ^ BIAS_BITS);
+        w[q] = __byte_perm(__byte_perm(r[4 * q], r[4 * q + 1], 0x0040), __byte_perm(r[4 * q + 2], r[4 * q + 3], 0x0040), 0x5410);
+    }
+    return ((s8[0] | s8[1]) | (s8[2] | s8[3])) | ((s8[4] | s8[5]) | (s8[6] | s8[7]));
+}
+// The same chunk with the exact clamp (any input).  Rare -- an element beyond the u8 range means that the
+// output scale does not fit the data -- so it is kept out of line and fetches the accumulators again from
+// tensor memory (the caller has not handed the accumulator back yet).  Called by whole warps.
+struct Words8 {
+    uint32_t w[8];
+};
+template <bool ROWS>
+__device__ __noinline__ Words8 chunk_to_u8_exact(uint32_t taddr, const int32_t *offs, const float *colf, uint32_t cl,
+    float num, float rs)
+{
+    uint32_t r[32];
+    tmem_ld32(taddr, r);
+    tmem_ld_wait(r);
+    Words8 out;
 #pragma unroll
     for (int j = 0; j < 32; j += 4) {
         const int4 o = *reinterpret_cast<const int4 *>(offs + cl + j);
@@ -169,23 +214,13 @@ __device__ __forceinline__ void chunk_to_u8(const int32_t *offs, const float *co
             c4.z = __fdiv_rn(num, __fmul_rn(rs, c4.z));
             c4.w = __fdiv_rn(num, __fmul_rn(rs, c4.w));
         }
-        const float g0 = __fmul_rn(__int2float_rn((int)r[j] + o.x), c4.x);
-        const float g1 = __fmul_rn(__int2float_rn((int)r[j + 1] + o.y), c4.y);
-        const float g2 = __fmul_rn(__int2float_rn((int)r[j + 2] + o.z), c4.z);
-        const float g3 = __fmul_rn(__int2float_rn((int)r[j + 3] + o.w), c4.w);
-        uint32_t u0 = __float_as_uint(__fadd_rn(g0, 12583040.0f));
-        uint32_t u1 = __float_as_uint(__fadd_rn(g1, 12583040.0f));
-        uint32_t u2 = __float_as_uint(__fadd_rn(g2, 12583040.0f));
-        uint32_t u3 = __float_as_uint(__fadd_rn(g3, 12583040.0f));
-        const uint32_t seen = (u0 ^ BIAS_BITS) | (u1 ^ BIAS_BITS) | (u2 ^ BIAS_BITS) | (u3 ^ BIAS_BITS);
-        if (__builtin_expect(seen > 255u, 0)) {
-            u0 = f32_to_u8_zp128(g0);
-            u1 = f32_to_u8_zp128(g1);
-            u2 = f32_to_u8_zp128(g2);
-            u3 = f32_to_u8_zp128(g3);
-        }
-        w[j >> 2] = __byte_perm(__byte_perm(u0, u1, 0x0040), __byte_perm(u2, u3, 0x0040), 0x5410);
+        const uint32_t b0 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j] + o.x), c4.x));
+        const uint32_t b1 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j + 1] + o.y), c4.y));
+        const uint32_t b2 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j + 2] + o.z), c4.z));
+        const uint32_t b3 = f32_to_u8_zp128(__fmul_rn(__int2float_rn((int)r[j + 3] + o.w), c4.w));
+        out.w[j >> 2] = __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
     }
+    return out;
 }
 // 32 bytes of row `lane` into the warp's staging box [32 rows][32 B], 32-byte swizzle: the 16-byte
 // chunk index is XORed with bit 2 of the row (address bit 7 into bit 4), the pattern the TMA store undoes
@@ -464,14 +499,7 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     } else {
                         mbar_expect_tx(&ctl->full[stage], tile_bytes);
                         tma_load_2d(&map_a, &ctl->full[stage], sa, (int)(kb * BLOCK_K), m0);
-                        if (p.balanced) {
-                            // the tile width varies: B arrives in boxes of 32 rows (4 KiB each)
-                            for (uint32_t u = 0; u < t.units; ++u) {
-                                tma_load_2d(&map_b, &ctl->full[stage], sb + u * 32 * BLOCK_K, (int)(kb * BLOCK_K), n0 + (int)(u * 32));
-                            }
-                        } else {
-                            tma_load_2d(&map_b, &ctl->full[stage], sb, (int)(kb * BLOCK_K), n0);
-                        }
+                        tma_load_2d(&map_b, &ctl->full[stage], sb, (int)(kb * BLOCK_K), n0);
                     }
                     if (++stage == p.stages) {
                         stage = 0;
@@ -660,7 +688,8 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             const bool have_next = walk.next(p, t_next);
             int32_t o_next[NQ];
             float sb_next[NQ];
-            if (have_next) {
+            const bool new_cols = have_next && (t_next.n0 != t.n0 || t_next.units != t.units);
+            if (new_cols) {
                 uint32_t cb, ce;
                 my_chunks(t_next.units, cb, ce);
                 fetch_raw(t_next.n0 + cb * 32, (ce - cb) * 32, o_next, sb_next);
@@ -684,22 +713,26 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             const uint32_t tbase = tmem_base + ((quad * 32u) << 16) + acc * MAX_BLOCK_N;
             if (c_begin >= c_end) {
                 release(acc);  // no columns of this tile: only the hand-back
-            } else if (KIND >= 0) {
-                // One 32-column chunk at a time (at most two per warp): the other three warps of the
-                // scheduler cover the tensor-memory read latency, and 32 live accumulators keep the
-                // warp within its register share.  The accumulator goes back to the MMA warp as soon
-                // as the last chunk has been read.
-                uint32_t ra[32];
+            } else if (KIND >= 2) {
+                // u8 output, one 32-column chunk at a time (at most two per warp; the other warps of the scheduler
+                // cover the tensor-memory read latency, and 32 live accumulators keep the warp within its register
+                // share).  The accumulator goes back to the MMA warp after the last chunk's range check (the rare
+                // exact conversion reads it again).
+                uint32_t ra[32], w[8];
                 for (uint32_t c = c_begin; c < c_end; ++c) {
                     const uint32_t cl = (c - c_begin) * 32;
                     tmem_ld32(tbase + c * 32, ra);
                     tmem_ld_wait(ra);
+                    const uint32_t seen = chunk_to_u8_quick<ROWS>(offs, colf, cl, ep.num, rs, ra, w);
+                    if (__any_sync(0xffffffffu, seen > 255u)) {
+                        const Words8 e = chunk_to_u8_exact<ROWS>(tbase + c * 32, offs, colf, cl, ep.num, rs);
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            w[q] = e.w[q];
+                        }
+                    }
                     if (c + 1 == c_end) {
                         release(acc);  // accumulator fully read: the MMA may reuse it
-                    }
-                    uint32_t w[8];
-                    if (KIND >= 2) {
-                        chunk_to_u8<ROWS>(offs, colf, cl, ep.num, rs, ra, w);
                     }
                     if (KIND == 3) {
                         // the previous box must have left the staging buffer
@@ -714,13 +747,23 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                             // rows beyond M are clipped by the tensor map
                             tma_store_2d(&map_c, stg, (int)(n0 + c * 32), (int)(m0 + quad * 32));
                         }
-                    } else if (KIND == 2) {
-                        if (row_ok) {
-                            uint8_t *out = reinterpret_cast<uint8_t *>(p.C) + (size_t)m * p.N + n0 + c * 32;
-                            *reinterpret_cast<uint4 *>(out) = make_uint4(w[0], w[1], w[2], w[3]);
-                            *reinterpret_cast<uint4 *>(out + 16) = make_uint4(w[4], w[5], w[6], w[7]);
-                        }
                     } else if (row_ok) {
+                        uint8_t *out = reinterpret_cast<uint8_t *>(p.C) + (size_t)m * p.N + n0 + c * 32;
+                        *reinterpret_cast<uint4 *>(out) = make_uint4(w[0], w[1], w[2], w[3]);
+                        *reinterpret_cast<uint4 *>(out + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+                    }
+                }
+            } else if (KIND >= 0) {
+                // s32 / f32 output: one 32-column chunk at a time
+                uint32_t ra[32];
+                for (uint32_t c = c_begin; c < c_end; ++c) {
+                    const uint32_t cl = (c - c_begin) * 32;
+                    tmem_ld32(tbase + c * 32, ra);
+                    tmem_ld_wait(ra);
+                    if (c + 1 == c_end) {
+                        release(acc);  // accumulator fully read: the MMA may reuse it
+                    }
+                    if (row_ok) {
                         store_chunk_fast<KIND, ROWS>(p.C, p.N, offs, colf, ep.num, rs, m, n0 + c * 32, cl, ra);
                     }
                 }
@@ -735,7 +778,7 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 }
                 release(acc);
             }
-            if (have_next) {
+            if (new_cols) {
                 __syncwarp();  // every lane is done reading this tile's constants
                 park(o_next, sb_next);
             }
@@ -1021,22 +1064,6 @@ EE launch_gemm_tcgen05(uint32_t M, uint32_t N, uint32_t K, const uint8_t *A, con
     const uint32_t block_m = pair ? 2 * BLOCK_M : BLOCK_M;
     p.tiles_m = (M + block_m - 1) / block_m;
     p.block_n = pick_block_n(p.tiles_m, N, pair ? pairs : c->sm_count);
-    // Equal spans of columns per SM instead of whole tiles when the last wave of whole tiles would be partly
-    // empty and the operands stay in L2 (the span walk has no L2 blocking); single CTAs only.
-    p.balanced = 0;
-    p.units_per_row = N / 32;
-    if (fast && !pair && (size_t)M * K + (size_t)N * K <= ((size_t)48 << 20)) {
-        const uint64_t units = (uint64_t)p.tiles_m * p.units_per_row;
-        const uint32_t whole = p.tiles_m * ((N + p.block_n - 1) / p.block_n);
-        const uint32_t waves = (whole + c->sm_count - 1) / c->sm_count;
-        // units on the busiest SM: whole tiles against equal spans
-        const uint64_t per_sm_whole = (uint64_t)waves * (p.block_n / 32);
-        const uint64_t per_sm_even = (units + c->sm_count - 1) / c->sm_count;
-        if (units >= (uint64_t)c->sm_count && per_sm_even * 10 <= per_sm_whole * 9) {
-            p.balanced = 1;
-            p.block_n = MAX_BLOCK_N;
-        }
-    }
     const uint32_t b_rows = pair ? p.block_n / 2 : p.block_n;
     p.stages = (uint32_t)(SMEM_RING_BYTES / (SMEM_A_STAGE + B200_ALIGN((size_t)b_rows * BLOCK_K, 1024)));
     if (p.stages > (uint32_t)MAX_STAGES) {
@@ -1047,12 +1074,12 @@ EE launch_gemm_tcgen05(uint32_t M, uint32_t N, uint32_t K, const uint8_t *A, con
 
     CUtensorMap map_a, map_b;
     if (!make_map(&map_a, A, K, M, K, BLOCK_M) ||
-        !make_map(&map_b, B, K, B200_ALIGN(N, 16), Kp, p.balanced ? 32u : b_rows)) {
+        !make_map(&map_b, B, K, B200_ALIGN(N, 16), Kp, b_rows)) {
         return NOT_SUPPORTED;
     }
     const uint32_t tiles = p.tiles_m * p.tiles_n;
     const uint32_t workers = pair ? (uint32_t)pairs : (uint32_t)c->sm_count;
-    const uint32_t grid = p.balanced ? workers : (tiles < workers ? tiles : workers) * (pair ? 2u : 1u);
+    const uint32_t grid = (tiles < workers ? tiles : workers) * (pair ? 2u : 1u);
     // u8 output: 32-row x 32-byte boxes, 32-byte swizzle, stored by TMA from the epilogue's staging
     CUtensorMap map_c = map_a;  // placeholder for the kinds that never touch it
     bool tma_c = false;
