@@ -188,6 +188,99 @@ def check_rows_against_numpy(stack, x, rows):
     return False
 
 
+def run_sharded_record(rank, world, lib, dist, stream, evict):
+    """The N-split of the FFN-shaped GEMM (K 8192, N 28672, per-channel weight scales, per-token activation
+    scales, u8 output) on `world` GPUs: every rank owns N / world output columns; the blocks are assembled on
+    every rank with an NCCL all-gather over NVLink.  Per M: this rank's GEMM alone, the all-gather alone, and
+    both with the gather of one row chunk overlapping the GEMM of the next; device times, maximum over ranks.
+    Rank 0 also runs the whole product on its own GPU: the strong-scaling reference and, for M <= 128, the
+    bytes the gathered result has to equal."""
+    import torch
+
+    from bolt_b200.sharded import ShardedFFN
+
+    K, N = 8192, 28672
+    ffn = ShardedFFN(rank, world, K, N)
+    one = None
+    if rank == 0:
+        # the unsplit problem on one GPU: all shards side by side
+        w = torch.cat([ffn.shard_weight(r) for r in range(world)], dim=1).contiguous()
+        one = ShardedFFN(0, 1, K, N, weight=w, like=ffn)
+        del w
+
+    def timed(fn, iters=7):
+        """median of `iters` device times (each after an L2 eviction), maximum over ranks"""
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(iters):
+            evict()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            fn()
+            b.record(stream)
+            b.synchronize()
+            ts.append(a.elapsed_time(b))
+        t = torch.tensor([sorted(ts)[len(ts) // 2]], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    rows = []
+    for M in (1, 128, 2048, 16384):
+        ms_c = timed(lambda: ffn.compute(M))
+        ms_g = timed(lambda: ffn.gather(M))
+        ms_o = timed(lambda: ffn.overlapped(M)) if M >= 2048 else None
+        ops = 2.0 * M * N * K
+        gathered = (world - 1) / world * M * N            # bytes every rank receives
+        row = {"M": M, "compute_ms": ms_c, "gather_ms": ms_g, "overlapped_ms": ms_o,
+               "compute_tops_all_gpus": ops / ms_c / 1e9,
+               "gather_GBps_in_per_gpu": gathered / ms_g / 1e6,
+               "end_to_end_ms": min(ms_o, ms_c + ms_g) if ms_o is not None else ms_c + ms_g}
+        row["end_to_end_mode"] = "overlapped" if ms_o is not None and ms_o < ms_c + ms_g else "compute then gather"
+        row["end_to_end_tops"] = ops / row["end_to_end_ms"] / 1e9
+        nvlink_ms = gathered / 770e9 * 1e3                 # measured peer-copy rate per direction on this pool
+        row["nvlink_roof_ms"] = nvlink_ms
+        row["limiter"] = ("collective latency" if M <= 128 else
+                          ("NVLink (gather longer than the GEMM)" if ms_g > ms_c else "tensor pipe (GEMM longer than the gather)"))
+        parity = None
+        if rank == 0:
+            t1 = []
+            for i in range(8):
+                evict()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                one.compute(M)
+                b.record(stream)
+                b.synchronize()
+                if i > 0:
+                    t1.append(a.elapsed_time(b))
+            row["one_gpu_ms"] = sorted(t1)[len(t1) // 2]
+            row["compute_speedup"] = row["one_gpu_ms"] / ms_c
+            row["compute_efficiency"] = row["compute_speedup"] / world
+            row["end_to_end_speedup"] = row["one_gpu_ms"] / row["end_to_end_ms"]
+        if M <= 128:
+            # gathered [M, N] on every rank against rank 0's single-GPU bytes
+            ffn.compute(M)
+            ffn.gather(M)
+            torch.cuda.synchronize()
+            ref = torch.empty(M * N, dtype=torch.uint8, device="cuda")
+            if rank == 0:
+                ref.copy_(one.block[: M * N])
+            dist.broadcast(ref, 0)
+            ok = torch.tensor([1 if torch.equal(ffn.assembled(M).reshape(-1), ref) else 0], device="cuda")
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            parity = bool(ok.item() == 1)
+        row["parity"] = parity
+        rows.append(row)
+    return {"workload": "ffn N-split: K=8192 N=28672 u8 out, per-channel / per-token scales, M=1 through the GEMV kernel",
+            "world": world, "columns_per_gpu": N // world, "rows": rows,
+            "mode": "gather = one all_gather_into_tensor of [M, N/world] u8 blocks into a shard-major buffer; "
+                    "overlapped = 4 row chunks, gather of chunk i on a side stream while chunk i+1 computes"}
+
+
 def run_b200_arm(args, rank, world, local_rank):
     import torch
 
@@ -301,7 +394,19 @@ def run_b200_arm(args, rank, world, local_rank):
         evict()
         stack.run_host(x_host, out_host)
     torch.cuda.synchronize()
-    e2e_s = max(time.perf_counter() - t0 - flush_s, 1e-9)
+    e2e_serial_s = max(time.perf_counter() - t0 - flush_s, 1e-9)
+    # the same steps with the copies of neighbouring steps overlapping the computation; every step still moves
+    # its input and its output across PCIe, and the 256 MiB eviction read stays inside (it is not subtracted)
+    from bolt_b200.linear_stack import HostPipeline
+    pipe = HostPipeline(stack)
+    n_e2e = max(args.steps, 20)
+    pipe.run([x_host] * 4, [out_host] * 4, step_fn=step_fn, before_step=evict)
+    barrier()
+    t0 = time.perf_counter()
+    pipe.run([x_host] * n_e2e, [out_host] * n_e2e, step_fn=step_fn, before_step=evict)
+    e2e_s = max((time.perf_counter() - t0) * args.steps / n_e2e, 1e-9)
+    e2e_ok = bool(check_rows_against_numpy(stack, x_host.numpy(), parity_rows)) and bool(
+        np.array_equal(out_host.numpy().reshape(M_TOKENS, -1)[parity_rows], stack.out_dev.cpu().numpy().reshape(M_TOKENS, -1)[parity_rows]))
     clocks = sampler.stop() if rank == 0 else None
     # the same step replayed back to back for about two seconds: what the stack sustains under the power limit
     sustained = None
@@ -327,12 +432,15 @@ def run_b200_arm(args, rank, world, local_rank):
                      "clocks": c2, "note": "no L2 eviction between steps (weights stay in L2), graph replays back to back"}
     status = lib.bolt_b200_device_status()
 
-    vals = torch.tensor([dev_s, gemm_s, e2e_s], dtype=torch.float64, device="cuda")
+    vals = torch.tensor([dev_s, gemm_s, e2e_s, e2e_serial_s], dtype=torch.float64, device="cuda")
     if dist is not None:
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
-    dev_s, gemm_s, e2e_s = [float(v) for v in vals.cpu()]
+    dev_s, gemm_s, e2e_s, e2e_serial_s = [float(v) for v in vals.cpu()]
     if dist is not None:
         dist.barrier()
+    sharded = None
+    if dist is not None and not args.no_sharded:
+        sharded = run_sharded_record(rank, world, lib, dist, stream, evict)
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -353,7 +461,11 @@ def run_b200_arm(args, rank, world, local_rank):
                    "device_status": status, "wall_s_timed_region": wall_s},
         "e2e": {"value": total_ops / e2e_s / 1e12, "unit": "TOP/s",
                 "h2d_bytes_per_step": M_TOKENS * HIDDEN * 4, "d2h_bytes_per_step": M_TOKENS * HIDDEN * 4,
-                "ms_per_step": e2e_s / args.steps * 1e3},
+                "ms_per_step": e2e_s / args.steps * 1e3,
+                "mode": "HostPipeline: H2D of step i+1 and D2H of step i-1 overlap step i; the eviction read is inside",
+                "output_checked": e2e_ok,
+                "serial_ms_per_step": e2e_serial_s / args.steps * 1e3,
+                "serial_value": total_ops / e2e_serial_s / 1e12},
         "gpu_launches": int(launches),
         "parity_checked": parity_ok,
         "parity_note": "%d of %d token rows of the step's fp32 output compared bit for bit with a numpy "
@@ -371,6 +483,8 @@ def run_b200_arm(args, rank, world, local_rank):
     }
     if sustained is not None:
         line["sustained"] = sustained
+    if sharded is not None:
+        line["sharded"] = sharded
     if base is not None:
         line["cpu_baseline"] = base
     print(json.dumps(line))
@@ -413,6 +527,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU leg (profiling runs)")
     ap.add_argument("--no-sustained", action="store_true", help="skip the two-second back-to-back replay")
+    ap.add_argument("--no-sharded", action="store_true", help="with --gpus > 1: skip the N-split FFN record")
     ap.add_argument("--workload", default="bert_stack",
                     help="bert_stack (the headline, default) or one of the side workloads: ffn, gemv, quantize, "
                          "resnet_conv, resnet_conv_u8, bnn, i8_peak (1 GPU, prints that workload's figures as one "

@@ -163,6 +163,56 @@ class LinearStack:
         torch.cuda.current_stream().synchronize()
 
 
+class HostPipeline:
+    """Steps fed from, and returned to, pinned host memory with the copies of neighbouring steps overlapping
+    the computation: the H2D copy of step i+1 and the D2H copy of step i-1 run on their own streams while
+    step i computes (two staging slots on the device, events between the three streams).  Every step still
+    moves its whole input and its whole output across PCIe."""
+
+    def __init__(self, stack):
+        torch = _torch()
+        self.stack = stack
+        self.h2d, self.d2h = torch.cuda.Stream(), torch.cuda.Stream()
+        self.x_stage = [torch.empty_like(stack.x_dev) for _ in range(2)]
+        self.o_stage = [torch.empty_like(stack.out_dev) for _ in range(2)]
+        self.ev_in = [torch.cuda.Event() for _ in range(2)]       # input of slot s has arrived
+        self.consumed = [torch.cuda.Event() for _ in range(2)]    # slot s's input has been taken over by the step
+        self.ev_out = [torch.cuda.Event() for _ in range(2)]      # slot s's output is staged
+        self.drained = [torch.cuda.Event() for _ in range(2)]     # slot s's output has left for the host
+        cur = torch.cuda.current_stream()
+        for e in self.consumed + self.drained:
+            e.record(cur)
+
+    def run(self, x_hosts, out_hosts, step_fn=None, before_step=None):
+        """x_hosts[i] -> step -> out_hosts[i] for every i; returns when the last output is on the host.
+        step_fn: what computes one step from stack.x_dev into stack.out_dev (default stack.step; a CUDA-graph
+        replay of it works too); before_step: optional hook enqueued on the compute stream before each step."""
+        torch = _torch()
+        st = self.stack
+        main = torch.cuda.current_stream()
+        step_fn = step_fn or st.step
+        for i, (xh, oh) in enumerate(zip(x_hosts, out_hosts)):
+            s = i & 1
+            self.h2d.wait_event(self.consumed[s])
+            with torch.cuda.stream(self.h2d):
+                self.x_stage[s].copy_(xh, non_blocking=True)
+                self.ev_in[s].record(self.h2d)
+            main.wait_event(self.ev_in[s])
+            main.wait_event(self.drained[s])
+            st.x_dev.copy_(self.x_stage[s], non_blocking=True)
+            self.consumed[s].record(main)
+            if before_step is not None:
+                before_step()
+            step_fn()
+            self.o_stage[s].copy_(st.out_dev, non_blocking=True)
+            self.ev_out[s].record(main)
+            self.d2h.wait_event(self.ev_out[s])
+            with torch.cuda.stream(self.d2h):
+                oh.copy_(self.o_stage[s], non_blocking=True)
+                self.drained[s].record(self.d2h)
+        self.d2h.synchronize()
+
+
 def bert_base_stack(M=4096, layers=12, hidden=768, inter=3072, per_channel=True, seed=100):
     """BERT-base-shaped linear stack: `layers` x (hidden -> inter -> hidden), weights ~N(0, 0.02)."""
     from . import synth

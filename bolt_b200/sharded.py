@@ -92,3 +92,122 @@ class ShardedLinear:
 
     def forward(self, a_dev, M, sA, out_dt, out_scale=1.0, group=None):
         return gather_columns(self.forward_local(a_dev, M, sA, out_dt, out_scale), M, self.N, group, self.align)
+
+
+# ---------------------------------------------------------------------------------------------------
+# Measurement of the N-split on the GPUs of one box (used by bench.py when it runs under torchrun).
+
+class ShardedFFN:
+    """The FFN-shaped product `[M, K] x [K, N]` (K 8192, N 28672 by default) with the weight's output
+    columns split over the ranks: s8 weights with one scale per output channel, u8 activations with one
+    scale per token, u8 (requantized) output.  Every rank generates the same activations and its own weight
+    columns from seeds, so no data has to be distributed before the timed region.
+
+    compute(M)            this rank's `[M, N / world]` block (GEMM on the tensor cores, GEMV kernel for M = 1)
+    gather(M)             all_gather_into_tensor of the blocks into a shard-major `[world][M][N / world]` buffer
+    overlapped(M, chunks) the rows are cut into chunks; chunk i is gathered on a side stream while chunk
+                          i + 1 is computed
+    """
+
+    def __init__(self, rank, world, K=8192, N=28672, max_m=16384, seed=7, weight=None, like=None):
+        """weight: s8 `[K, N / world]` on the device instead of the generated shard; like: another
+        ShardedFFN whose activations and token scales are shared."""
+        import torch
+
+        from . import (DF_NORMAL, DT_I8, lib, matrix_matrix_multiply_transform_rhs, matrix_matrix_multiply_transform_rhs_bytes,
+                       tensor2df)
+
+        assert N % (32 * world) == 0
+        self.rank, self.world, self.K, self.N = rank, world, K, N
+        self.nloc = N // world
+        self.max_m = max_m
+        self.torch = torch
+        self.lib = lib()
+        self.w_gen_seed = seed
+        w = self.shard_weight(rank) if weight is None else weight
+        desc = tensor2df(DT_I8, DF_NORMAL, K, self.nloc)
+        nbytes, self.rhs = matrix_matrix_multiply_transform_rhs_bytes(desc)
+        self.packed = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+        matrix_matrix_multiply_transform_rhs(desc, C.c_void_p(w.data_ptr()), C.c_void_p(self.packed.data_ptr()))
+        torch.cuda.synchronize()
+        del w
+        if like is None:
+            g = torch.Generator("cuda").manual_seed(seed + 1000)
+            self.a = torch.randint(0, 256, (max_m, K), dtype=torch.uint8, device="cuda", generator=g)
+            self.rs = (torch.rand(max_m, device="cuda", generator=g) * 20 + 30).float()
+        else:
+            self.a, self.rs = like.a, like.rs
+        self.sB = self.channel_scales()[rank * self.nloc:(rank + 1) * self.nloc].contiguous()
+        self.block = torch.empty(max_m * self.nloc, dtype=torch.uint8, device="cuda")
+        self.full = torch.empty(world * max_m * self.nloc, dtype=torch.uint8, device="cuda")
+        self.y32 = torch.zeros(self.nloc, dtype=torch.int32, device="cuda")
+        self.side = torch.cuda.Stream()
+
+    def shard_weight(self, r):
+        """s8 `[K, N / world]`: the columns of rank r (every rank can regenerate any shard)"""
+        torch = self.torch
+        g = torch.Generator("cuda").manual_seed(self.w_gen_seed * 100 + r)
+        return torch.randint(-127, 128, (self.K, self.nloc), dtype=torch.int8, device="cuda", generator=g)
+
+    def channel_scales(self):
+        torch = self.torch
+        g = torch.Generator("cuda").manual_seed(self.w_gen_seed + 2000)
+        return (torch.rand(self.N, device="cuda", generator=g) * 500 + 1500).float()
+
+    def compute(self, M, row0=0, rows=None):
+        """rows [row0, row0 + rows) of this rank's block"""
+        from . import CHECK_STATUS, DF_NKN32K4, DT_I8, DT_U8_Q, GemmEpilogue
+
+        rows = M if rows is None else rows
+        L = self.lib
+        out = C.c_void_p(self.block.data_ptr() + row0 * self.nloc)
+        if M == 1:
+            # M = 1 goes through the GEMV kernel (per-tensor scales: the reference's protocol), packed layout shared
+            scale = (C.c_float * 2)(-1.0, 0.0005)
+            CHECK_STATUS(L.mvm_cuda_b200(self.nloc, self.K, DT_I8, DF_NKN32K4, C.c_void_p(self.packed.data_ptr()),
+                                         C.c_void_p(self.a.data_ptr()), out, C.c_void_p(self.packed.data_ptr() + self.rhs),
+                                         C.cast(scale, C.POINTER(C.c_float))), "mvm")
+            return
+        ep = GemmEpilogue()
+        ep.out_dt, ep.accumulate, ep.out_scale, ep.sA, ep.sB = DT_U8_Q, 0, 40.0, 1.0, 1.0
+        ep.row_scale = C.c_void_p(self.rs.data_ptr() + 4 * row0)
+        ep.col_scale = C.c_void_p(self.sB.data_ptr())
+        CHECK_STATUS(L.bolt_b200_gemm_u8s8_ex(self.nloc, rows, self.K, C.c_void_p(self.a.data_ptr() + row0 * self.K),
+                                              C.c_void_p(self.packed.data_ptr()), C.c_void_p(self.packed.data_ptr() + self.rhs),
+                                              out, C.byref(ep)), "gemm")
+
+    def gather(self, M, row0=0, rows=None):
+        import torch.distributed as dist
+
+        rows = M if rows is None else rows
+        src = self.block[row0 * self.nloc:(row0 + rows) * self.nloc]
+        if row0 == 0 and rows == M:
+            dst = self.full[: self.world * M * self.nloc]
+        else:
+            # chunked: every chunk gets its own shard-major slot [world][rows][nloc]
+            dst = self.full[self.world * row0 * self.nloc: self.world * (row0 + rows) * self.nloc]
+        dist.all_gather_into_tensor(dst, src)
+
+    def overlapped(self, M, chunks=4):
+        torch = self.torch
+        main = torch.cuda.current_stream()
+        per = -(-M // chunks)
+        per = max(128, -(-per // 128) * 128)
+        evs = []
+        r0 = 0
+        while r0 < M:
+            rows = min(per, M - r0)
+            self.compute(M, r0, rows)
+            ev = torch.cuda.Event()
+            ev.record(main)
+            self.side.wait_event(ev)
+            with torch.cuda.stream(self.side):
+                self.gather(M, r0, rows)
+            r0 += rows
+        done = torch.cuda.Event()
+        done.record(self.side)
+        main.wait_event(done)
+
+    def assembled(self, M):
+        """`[M, N]` from the shard-major gather buffer (after gather(M))"""
+        return self.full[: self.world * M * self.nloc].view(self.world, M, self.nloc).permute(1, 0, 2).reshape(M, self.N)
