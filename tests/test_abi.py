@@ -1,6 +1,7 @@
 """The C-ABI library loads without a GPU and exports every symbol include/bolt_b200.h declares;
 the byte-count and format entry points (pure host arithmetic) follow the reference's formulas."""
 import ctypes as C
+import os
 import re
 
 import bolt_b200 as B
@@ -112,3 +113,39 @@ def test_infer_output_size_rule():
         assert False
     except B.BoltError as e:
         assert e.code == B.NOT_SUPPORTED
+
+
+def _abi_values(tmp_path, extra):
+    import subprocess
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = str(tmp_path / ("abi" + str(len(extra))))
+    subprocess.check_call(["g++", "-std=c++11", "-w", "-I", os.path.join(root, "include")] + extra +
+                          [os.path.join(root, "integration", "abi_print.cpp"), "-o", exe])
+    return subprocess.check_output([exe]).decode()
+
+
+def test_header_types_match_bolts_headers(tmp_path):
+    """Sizes, field offsets and enumerator values of everything that crosses the C ABI: the stand-in typedefs of
+    include/bolt_b200.h against the values printed by the same program built on Bolt's own headers
+    (common/uni/include: sys.h, error.h, tensor_desc.h, parameter_spec.h), kept in golden/abi_values.txt."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    with open(os.path.join(root, "tests", "golden", "abi_values.txt")) as f:
+        pinned = f.read()
+    assert _abi_values(tmp_path, []) == pinned
+    bolt_root = os.environ.get("BOLT_ROOT") or os.path.join(os.path.dirname(root), "reference")
+    uni = os.path.join(bolt_root, "common", "uni", "include")
+    if os.path.isdir(uni):
+        # the fixture itself is still what Bolt's headers say
+        assert _abi_values(tmp_path, ["-include", "cstdint", "-DBOLT_B200_WITH_BOLT_HEADERS", "-I", uni]) == pinned
+    # the ctypes mirrors used by the Python host side
+    import bolt_b200 as B
+    vals = dict(line.split(" = ") for line in pinned.strip().splitlines())
+    assert C.sizeof(B.TensorDesc) == int(vals["sizeof(TensorDesc)"])
+    assert C.sizeof(B.ConvolutionParamSpec) == int(vals["sizeof(ConvolutionParamSpec)"])
+    assert C.sizeof(B.ActivationParamSpec) == int(vals["sizeof(ActivationParamSpec)"])
+    assert B.ConvolutionParamSpec.round_mode.offset == int(vals["offsetof(ConvolutionParamSpec, round_mode)"])
+    for name in ("DT_U8_Q", "DT_I8", "DT_I32", "DT_F32", "DT_BIN01", "DT_BIN11", "DF_NCHWC8", "DF_NCHWC16", "DF_NKN32K4",
+                 "DF_NKNxKx", "DF_NCHWC2NxC4", "DF_TRANSPOSE", "DF_NORMAL", "CONVOLUTION_ALGORITHM_POINTWISE",
+                 "CONVOLUTION_ALGORITHM_DIRECT", "CONVOLUTION_ALGORITHM_BNN"):
+        assert getattr(B, name) == int(vals[name]), name
