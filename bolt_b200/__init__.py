@@ -112,6 +112,7 @@ SIGNATURES = {
     "bolt_b200_set_device": (C.c_int, [C.c_int]),
     "bolt_b200_use_para": (C.c_int, [_vp]),
     "bolt_b200_i8_mma_rate": (C.c_int, [C.c_uint32, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
+    "bolt_b200_selftest_wait_limit": (C.c_int, [C.c_uint32]),
     "bolt_b200_set_stream": (C.c_int, [_vp]),
     "bolt_b200_synchronize": (C.c_int, []),
     "bolt_b200_device_status": (C.c_int, []),

@@ -85,6 +85,20 @@ __global__ void __launch_bounds__(128, 1) i8_mma_rate_kernel(uint32_t iters, int
     }
 }
 
+// One CTA, one barrier that expects an arrival nobody makes: the bounded wait has to give up after
+// `limit_cycles`, record it in the status word and return, leaving the context usable.
+__global__ void wait_runs_out_kernel(long long limit_cycles, int *status)
+{
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (!mbar_wait_limit(&bar, 0, limit_cycles)) {
+            atomicExch(status, 21);
+        }
+    }
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -126,5 +140,20 @@ extern "C" EE bolt_b200_i8_mma_rate(U32 mma_per_sm, F32 *milliseconds, F32 *tops
     B200_CUDA(err);
     *milliseconds = ms;
     *tops = (float)((double)c->sm_count * mma_per_sm * 2.0 * tc::BLOCK_M * PROBE_N * tc::UMMA_K / (ms * 1e-3) / 1e12);
+    return SUCCESS;
+}
+
+extern "C" EE bolt_b200_selftest_wait_limit(U32 limit_cycles)
+{
+    DeviceCtx *c = ctx();
+    if (c == nullptr) {
+        return UNKNOWN;
+    }
+    if (limit_cycles == 0 || limit_cycles > 2000000000u) {
+        return NOT_MATCH;  // at most about a second
+    }
+    wait_runs_out_kernel<<<1, 32, 0, tls().stream>>>((long long)limit_cycles, c->d_status);
+    count_launch(1);
+    B200_CUDA(cudaGetLastError());
     return SUCCESS;
 }

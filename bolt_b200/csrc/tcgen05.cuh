@@ -57,7 +57,7 @@ __device__ __forceinline__ void prefetch_l2_bulk(const void *p, uint32_t bytes)
 // Bounded wait: false when the limit ran out (the caller then aborts the CTA's work).  The bound is
 // counted in SM clock cycles (clock64 is a plain register read; the global nanosecond timer costs
 // about a microsecond per read and must stay off this path, every role waits several times per tile).
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t *bar, uint32_t parity, long long limit_cycles)
 {
     if (mbar_try_wait(bar, parity)) {
         return true;
@@ -70,10 +70,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
                 return true;
             }
         }
-        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+        if (clock64() - t0 > limit_cycles) {
             return false;
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
+{
+    return mbar_wait_limit(bar, parity, WAIT_LIMIT_CYCLES);
 }
 __device__ __forceinline__ void tma_load_2d(const CUtensorMap *map, uint64_t *bar, void *dst, int x, int y)
 {

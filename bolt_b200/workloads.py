@@ -196,8 +196,8 @@ def gemv(peaks, iters=20):
 
 
 def quantize(peaks, iters=20):
-    """stand-alone quantize / requantize / dequantize on a 16384 x 3072 tensor (four config-2
-    activations: 201 MB of fp32, larger than L2)."""
+    """stand-alone quantize / requantize / dequantize on a 16384 x 3072 tensor (four batches of
+    4096 x 3072 activations: 201 MB of fp32, larger than L2)."""
     torch = _torch()
     L, tm = lib(), Timer()
     n = 16384 * 3072

@@ -197,6 +197,12 @@ EE bolt_b200_release_weight(const void *host_packed);
  * compared with.  Blocks until the run is over; a short run (a millisecond) gives the burst figure, one of
  * seconds the figure under the board's power limit. */
 EE bolt_b200_i8_mma_rate(U32 mma_per_sm, F32 *milliseconds, F32 *tops);
+/* Self-test of the bounded waits every kernel of this library uses on its barriers: launches one block
+ * that waits, with a limit of `limit_cycles` SM cycles (1 .. 2e9), on a barrier nobody arrives on.  The
+ * wait gives up, the kernel stores 21 in the device status word and returns; the next
+ * bolt_b200_synchronize() therefore returns UNKNOWN (and clears the word), and later calls work as
+ * before.  No counterpart in the reference. */
+EE bolt_b200_selftest_wait_limit(U32 limit_cycles);
 /* Number of kernels this library has launched in this process (all threads). */
 uint64_t bolt_b200_launch_count(void);
 /* 1 if the u8 x s8 tensor-core (tcgen05) GEMM was used by the last GEMM call of this thread. */

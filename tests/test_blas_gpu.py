@@ -136,8 +136,8 @@ def test_mmm_tensor_core_shapes(m, n, k):
     assert same_bits(mmm_gpu(A, Bm, [0.5], Cbits), O.port_gemm(A, Bm, off, [0.5], Cbits))
 
 
-def test_mmm_config1_dynamic_quant_fp32_out():
-    """BASELINE config 1: A fp32 [128,768] ~N(0,1) -> dynamic U8_Q, B ~N(0,0.02) -> I8 per tensor,
+def test_mmm_small_projection_dynamic_quant_fp32_out():
+    """The CPU-runnable case: A fp32 [128,768] ~N(0,1) -> dynamic U8_Q, B ~N(0,0.02) -> I8 per tensor,
     pre-packed, fp32 dequantized output; fp32 output within 1e-5 relative (here: bit-equal)."""
     m, k, n = 128, 768, 768
     Af = synth.normal(1, (m, k))
@@ -339,7 +339,7 @@ def test_mvm_cover_sweep_vs_oracle():
 
 
 def test_mvm_large_vs_oracle():
-    """An FFN-shaped slice: K = 8192, N = 4096 (1/7 of config 4's N), all epilogues."""
+    """An FFN-shaped slice: K = 8192, N = 4096 (1/7 of the FFN's 28672 columns), all epilogues."""
     n, k = 4096, 8192
     W, x = synth.s8(51, (n, k)), synth.u8(52, (k,))
     off = O.port_offsetc(W, True)

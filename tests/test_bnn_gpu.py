@@ -95,7 +95,7 @@ def test_bnn_vs_oracle(shape, xnor):
     assert got.tobytes() == ref.tobytes()
 
 
-def test_bnn_config5_slice_and_host_pointers():
+def test_bnn_benchmarked_geometry_and_host_pointers():
     """The benchmarked geometry (C 256 -> 256, 28 x 28, 3 x 3, pad 1) at batch 2, both modes."""
     shape = (2, 256, 28, 28, 256, 3, 3, 1, 1)
     for xnor in (True, False):

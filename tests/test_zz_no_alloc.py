@@ -17,6 +17,7 @@ import numpy as np
 import pytest
 
 sys.path.insert(0, os.path.dirname(__file__))
+import oracle as O  # noqa: E402
 import bolt_b200 as B  # noqa: E402
 from bolt_b200 import synth  # noqa: E402
 from util import dev_zeros, dptr, to_dev, to_host  # noqa: E402
@@ -50,6 +51,28 @@ def test_noalloc_matches_regular_path_twice_in_a_row():
         q_ref, s_ref = regular_path(x)
         assert s_new.tobytes() == s_ref.tobytes()
         assert q_new.tobytes() == q_ref.tobytes()
+
+
+def test_noalloc_matches_the_cpu_oracle_and_allocates_nothing():
+    """Against the scalar restatement of the reference's quantize (dynamic scale = 127 / absmax), and with the
+    device's free memory read before and after the second call: the call must not change it."""
+    import torch
+
+    lib = B.lib()
+    for seed, n, std in ((903, 3 * 1000 * 1000 + 7, 1.5), (904, 70001, 40.0)):
+        x = synth.normal(seed, (n,), std)
+        q_ref, s_ref = np.zeros(n, np.uint8), np.array([-1.0], np.float32)
+        O.port.oracle_quantize_f32_u8(O.ptr(x), n, O.ptr(q_ref), O.ptr(s_ref), 0)
+        dx, dq, ds = to_dev(x), dev_zeros(n), dev_zeros(16)
+        B.CHECK_STATUS(lib.bolt_b200_quantize_f32_u8_noalloc(dptr(dx), n, dptr(dq), dptr(ds)), "first call")
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
+        B.CHECK_STATUS(lib.bolt_b200_quantize_f32_u8_noalloc(dptr(dx), n, dptr(dq), dptr(ds)), "second call")
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        assert free_after == free_before, (free_before, free_after)
+        assert to_host(ds, np.float32, 1).tobytes() == s_ref.tobytes()
+        assert to_host(dq, np.uint8, n).tobytes() == q_ref.tobytes()
 
 
 def test_noalloc_edges():
