@@ -113,6 +113,10 @@ SIGNATURES = {
     "bolt_b200_use_para": (C.c_int, [_vp]),
     "bolt_b200_i8_mma_rate": (C.c_int, [C.c_uint32, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "bolt_b200_selftest_wait_limit": (C.c_int, [C.c_uint32]),
+    "matmul_infer_output_size_cuda_b200": (C.c_int, [_TDp, C.c_int, _TDp, C.c_int, _TDp]),
+    "matmul_infer_forward_tmp_bytes_cuda_b200": (C.c_int, [_TDp, C.c_int, _TDp, C.c_int, _TDp, C.c_float, C.POINTER(C.c_uint32)]),
+    "matmul_cuda_b200": (C.c_int, [_TDp, C.c_int, _vp, C.c_float, _TDp, C.c_int, _vp, C.c_float, _TDp, _vp, C.c_uint32, _vp,
+                                   _TDp, _vp, C.POINTER(C.c_float)]),
     "bolt_b200_set_stream": (C.c_int, [_vp]),
     "bolt_b200_synchronize": (C.c_int, []),
     "bolt_b200_device_status": (C.c_int, []),
@@ -272,6 +276,40 @@ def dequantize(qDesc, qData, scale, dDesc, dData):
     b = tensor1d(DT_F32, 0)
     CHECK_STATUS(lib().dequantize_cuda_b200(C.byref(qDesc), qData, C.cast(arr, _f32p), C.byref(b), None,
                                             C.byref(dDesc), dData), "dequantize")
+
+
+# ---- matmul (compute/tensor/include/tensor_computing.h: matmul_infer_output_size, _tmp_bytes, matmul) -----
+def tensor_nd(dt, shape):
+    """desc of a row-major array of `shape` (outermost first); Bolt keeps the innermost extent in dims[0]"""
+    d = TensorDesc()
+    d.dt, d.nDims = dt, len(shape)
+    d.df = DF_NORMAL if len(shape) == 2 else DF_NCHW
+    for i, s in enumerate(reversed(shape)):
+        d.dims[i] = s
+    return d
+
+
+def matmul_infer_output_size(aDesc, transposeA, bDesc, transposeB):
+    c = TensorDesc()
+    CHECK_STATUS(lib().matmul_infer_output_size_cuda_b200(C.byref(aDesc), int(transposeA), C.byref(bDesc), int(transposeB),
+                                                          C.byref(c)), "matmul_infer_output_size")
+    return c
+
+
+def matmul_infer_forward_tmp_bytes(aDesc, transposeA, bDesc, transposeB, cDesc, c_scale):
+    n = C.c_uint32(0)
+    CHECK_STATUS(lib().matmul_infer_forward_tmp_bytes_cuda_b200(C.byref(aDesc), int(transposeA), C.byref(bDesc), int(transposeB),
+                                                                C.byref(cDesc), c_scale, C.byref(n)), "matmul tmp_bytes")
+    return n.value
+
+
+def matmul(aDesc, transposeA, A, a_scale, bDesc, transposeB, Bp, b_scale, bias_desc, bias, tmp_bytes, tmp, cDesc, Cp, c_scale):
+    """returns the output tensor's scale after the call (Tensor::get_scale of C)"""
+    s = C.c_float(c_scale)
+    bd = bias_desc if bias_desc is not None else tensor1d(DT_F32, 0)
+    CHECK_STATUS(lib().matmul_cuda_b200(C.byref(aDesc), int(transposeA), A, a_scale, C.byref(bDesc), int(transposeB), Bp, b_scale,
+                                        C.byref(bd), bias, tmp_bytes, tmp, C.byref(cDesc), Cp, C.byref(s)), "matmul")
+    return s.value
 
 
 # ---- convolution (compute/tensor/include/tensor_computing.h:26-64) --------------------------

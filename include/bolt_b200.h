@@ -400,6 +400,26 @@ EE bolt_b200_convolution_ex(const TensorDesc *inputDesc, void *input, void *eltw
     const TensorDesc *outputDesc, void *output, const ActivationParamSpec *activationDesc,
     const bolt_b200_conv_ext *ext);
 
+/* ---- matmul: the int8 branch of Bolt's operator (compute/tensor/src/matmul.cpp:303-557) ------------------
+ * Both operands are activations: fp32 ones are quantized per call (A to U8_Q and B to I8; when the result
+ * is a row or a column, A to I8 and B to U8_Q: matmul.cpp:373-398), B is packed on the fly for every batch
+ * (mmm.cpp:208-219), leading dimensions broadcast (matmul.cpp:489-517).  aScale / bScale / *cScale stand for
+ * Tensor::get_scale() of the three tensors: a scale <= 0 asks for 127 / absmax; for an operand that is
+ * already quantized it is the scale its bytes carry.  The output is DT_F32 (the int8 path is taken when
+ * (I32)*cScale != 0 or an operand is quantized) or DT_U8_Q (requantized inside the product when *cScale > 0,
+ * else quantized dynamically from the fp32 product, *cScale receiving the scale: matmul.cpp:535-547).
+ * `bias`, if given, is repeated over the product's bytes before the multiplication, which accumulates on
+ * top of them as the reference does (matmul.cpp:453-466).  Replaces matmul_infer_output_size_cpu,
+ * matmul_infer_forward_tmp_bytes and matmul for Arch CUDA_B200. */
+EE matmul_infer_output_size_cuda_b200(const TensorDesc *matrixADesc, int transposeA,
+    const TensorDesc *matrixBDesc, int transposeB, TensorDesc *matrixCDesc);
+EE matmul_infer_forward_tmp_bytes_cuda_b200(const TensorDesc *matrixADesc, int transposeA,
+    const TensorDesc *matrixBDesc, int transposeB, const TensorDesc *matrixCDesc, F32 cScale, U32 *bytes);
+EE matmul_cuda_b200(const TensorDesc *matrixADesc, int transposeA, const void *matrixA, F32 aScale,
+    const TensorDesc *matrixBDesc, int transposeB, const void *matrixB, F32 bScale,
+    const TensorDesc *biasDesc, const void *bias, U32 tmpBytes, void *tmp,
+    const TensorDesc *matrixCDesc, void *matrixC, F32 *cScale);
+
 /* ============================== 3. operators ================================================= */
 /* Bolt's public signatures (compute/blas_enhance/include/blas_enhance.h:21-88); arch must be
  * CUDA_B200, anything else returns NOT_SUPPORTED.  Argument checks follow mmm.cpp:161-197 and

@@ -271,3 +271,102 @@ def ref_bnn_conv(shape, xnor, xin, wbits, scale, bias):
                               ptr(scale), ptr(bias), ptr(out))
     assert rc == 0
     return out
+
+
+# ---- the matmul operator (compute/tensor/src/matmul.cpp:303-557, x86 int8 branch) -------------------
+_NP_OF_DT = {DT_F32: np.float32, DT_U8_Q: np.uint8, DT_I8: np.int8}
+
+
+def _quant_operand(x, dt_in, scale_in, dt_want):
+    """matmul.cpp:401-421: an operand that is not of the wanted type is quantized (whole tensor, one scale)"""
+    if dt_in == dt_want:
+        return x, np.float32(scale_in)
+    assert dt_in == DT_F32
+    q = np.zeros(x.size, np.uint8 if dt_want == DT_U8_Q else np.int8)
+    s = np.array([scale_in], np.float32)
+    fn = port.oracle_quantize_f32_u8 if dt_want == DT_U8_Q else port.oracle_quantize_f32_i8
+    fn(ptr(np.ascontiguousarray(x.reshape(-1))), x.size, ptr(q), ptr(s), 0)
+    return q.reshape(x.shape), s[0]
+
+
+def port_matmul(A, a_dt, a_scale, tA, B, b_dt, b_scale, tB, bias, c_dt, c_scale):
+    """Restatement of the operator from the scalar primitives.  A, B: numpy arrays of rank >= 2 (outermost
+    first).  Returns (C, scale of C after the call)."""
+    a2 = A.shape[-2:][::-1] if tA else A.shape[-2:]
+    b2 = B.shape[-2:][::-1] if tB else B.shape[-2:]
+    M, K = a2
+    K2, N = b2
+    assert K == K2
+    nd = max(A.ndim, B.ndim)
+    ash = (1,) * (nd - A.ndim) + A.shape
+    bsh = (1,) * (nd - B.ndim) + B.shape
+    batch = tuple(max(x, y) for x, y in zip(ash[:-2], bsh[:-2]))
+    is_mvm = M == 1 or N == 1
+    qa_dt, qb_dt = (DT_I8, DT_U8_Q) if is_mvm else (DT_U8_Q, DT_I8)
+    qA, sA = _quant_operand(A, a_dt, a_scale, qa_dt)
+    qB, sB = _quant_operand(B, b_dt, b_scale, qb_dt)
+    scaleO = np.float32(np.float32(1) * sA) * sB
+    static_u8 = c_dt == DT_U8_Q and c_scale > 0
+    if static_u8:
+        scale = [-1.0, float(np.float32(c_scale) / scaleO)]
+        prod_dt = np.uint8
+    else:
+        scale = [float(scaleO)]
+        prod_dt = np.float32
+    qA = qA.reshape(ash)
+    qB = qB.reshape(bsh)
+    out = np.zeros(batch + (M, N), prod_dt)
+    if bias is not None:
+        flat = out.reshape(-1).view(np.uint8)
+        bb = np.ascontiguousarray(bias).view(np.uint8)
+        flat[:] = np.tile(bb, flat.size // bb.size)
+    for idx in np.ndindex(*batch):
+        ia = tuple(i if i < d else 0 for i, d in zip(idx, ash[:-2]))
+        ib = tuple(i if i < d else 0 for i, d in zip(idx, bsh[:-2]))
+        a, b = np.ascontiguousarray(qA[ia]), np.ascontiguousarray(qB[ib])
+        c_in = out[idx]
+        if M == 1:
+            # the u8 matrix is B seen as [N, K]; stored [K, N] unless transposeB
+            y = np.ascontiguousarray(c_in.reshape(-1)).copy()
+            s = _scale_arr(scale)
+            port.oracle_gemv_u8s8_row(N, K, ptr(b), int(not tB), ptr(np.ascontiguousarray(a.reshape(-1))), ptr(y), ptr(s))
+            out[idx] = y.reshape(M, N)
+        elif N == 1:
+            # the s8 matrix is A seen as [M, K]
+            offc = port_offsetc(a, not tA)
+            y = port_gemv(a, np.ascontiguousarray(b.reshape(-1)), offc, scale, np.ascontiguousarray(c_in.reshape(-1)), w_t=bool(tA))
+            out[idx] = y.reshape(M, N)
+        else:
+            offc = port_offsetc(b, bool(tB))
+            cin = c_in if prod_dt is np.uint8 else c_in.view(np.int32)
+            r = port_gemm(a, b, offc, scale, np.ascontiguousarray(cin), a_t=bool(tA), b_t=bool(tB))
+            out[idx] = r if prod_dt is np.uint8 else r.view(np.float32)
+    if c_dt == DT_U8_Q and not static_u8:
+        q = np.zeros(out.size, np.uint8)
+        s = np.array([c_scale], np.float32)
+        port.oracle_quantize_f32_u8(ptr(np.ascontiguousarray(out.reshape(-1))), out.size, ptr(q), ptr(s), 0)
+        return q.reshape(out.shape), float(s[0])
+    return out, float(c_scale)
+
+
+def ref_matmul(A, a_dt, a_scale, tA, B, b_dt, b_scale, tB, bias, c_dt, c_scale):
+    """The reference's own `matmul` (through ref_matmul_shim.cpp).  Returns (status, C, scale of C)."""
+    f = ref.ref_matmul
+    f.argtypes = [_i32, _u32, _vp, _c.c_float, _i32, _vp, _i32, _u32, _vp, _c.c_float, _i32, _vp, _u32, _vp,
+                  _i32, _c.c_float, _vp, _u64, _vp, _vp, _vp]
+    ad = (_u32 * A.ndim)(*A.shape)
+    bd = (_u32 * B.ndim)(*B.shape)
+    a2 = A.shape[-2:][::-1] if tA else A.shape[-2:]
+    b2 = B.shape[-2:][::-1] if tB else B.shape[-2:]
+    nd = max(A.ndim, B.ndim)
+    batch = tuple(max(x, y) for x, y in zip((1,) * (nd - A.ndim) + A.shape[:-2], (1,) * (nd - B.ndim) + B.shape[:-2]))
+    n_out = int(np.prod(batch + (a2[0], b2[1])))
+    buf = np.zeros(n_out * 4 + 256, np.uint8)
+    cnd, cdims, cs = _u32(), (_u32 * 8)(), _c.c_float()
+    rc = f(a_dt, A.ndim, ad, a_scale, int(tA), ptr(A), b_dt, B.ndim, bd, b_scale, int(tB), ptr(B),
+           0 if bias is None else bias.size, ptr(bias), c_dt, c_scale, ptr(buf), buf.size, _c.byref(cnd), cdims, _c.byref(cs))
+    if rc != 0:
+        return rc, None, None
+    shape = tuple(cdims[i] for i in range(cnd.value))
+    npdt = np.float32 if c_dt == DT_F32 else np.uint8
+    return 0, buf[: n_out * np.dtype(npdt).itemsize].view(npdt).reshape(shape).copy(), float(cs.value)

@@ -146,3 +146,50 @@ def bnn_inputs(i, xnor, scaling):
         scale = np.abs(wf).reshape(oc, -1).mean(axis=1).astype(np.float16)
         bias = synth.normal(seed + 2, (oc,), 0.1).astype(np.float16)
     return to_blocked(x.view(np.uint16), 8), wbits, scale.view(np.uint16), bias.view(np.uint16)
+
+
+# ---- matmul operator -------------------------------------------------------------------------------
+# data types as Bolt numbers them
+MM_F32, MM_U8, MM_I8 = 6, 10, 1
+# name -> (A shape, A type, A scale, transposeA, B shape, B type, B scale, transposeB, bias length, C type, C scale).
+# Shapes are the stored shapes, outermost first.  A scale <= 0 on an fp32 tensor asks for 127 / absmax.  Every case
+# writes fp32 or dynamically quantized u8, or is a one-row product: the reference's GEMM with a u8 result of
+# more than one row stores its rows 4N bytes apart (past the end of the tensor), so there is nothing to pin there.
+MATMUL_CASES = {
+    "f32": ((2, 3, 40, 64), MM_F32, -1, 0, (2, 3, 64, 24), MM_F32, -1, 0, 0, MM_F32, -1),
+    "u8dyn": ((2, 3, 40, 64), MM_F32, -1, 0, (2, 3, 64, 24), MM_F32, -1, 0, 0, MM_U8, -1),
+    "row": ((2, 3, 1, 64), MM_F32, -1, 0, (2, 3, 64, 24), MM_F32, -1, 0, 0, MM_F32, -1),
+    "row_tb": ((2, 3, 1, 64), MM_F32, -1, 0, (2, 3, 24, 64), MM_F32, -1, 1, 0, MM_F32, -1),
+    "row_u8": ((4, 1, 96), MM_F32, -1, 0, (4, 96, 50), MM_F32, -1, 0, 0, MM_U8, 0.7),
+    "row_u8dyn": ((4, 1, 96), MM_F32, -1, 0, (4, 96, 50), MM_F32, -1, 0, 0, MM_U8, -1),
+    "col": ((2, 3, 40, 64), MM_F32, -1, 0, (2, 3, 64, 1), MM_F32, -1, 0, 0, MM_F32, -1),
+    "col_ta": ((2, 3, 64, 40), MM_F32, -1, 1, (2, 3, 64, 1), MM_F32, -1, 0, 0, MM_F32, -1),
+    "tb": ((2, 3, 40, 64), MM_F32, -1, 0, (2, 3, 24, 64), MM_F32, -1, 1, 0, MM_F32, -1),
+    "ta": ((2, 3, 64, 40), MM_F32, -1, 1, (2, 3, 64, 24), MM_F32, -1, 0, 0, MM_F32, -1),
+    "ta_tb": ((2, 3, 64, 40), MM_F32, -1, 1, (2, 3, 24, 64), MM_F32, -1, 1, 0, MM_F32, -1),
+    "bias": ((2, 3, 40, 64), MM_F32, -1, 0, (2, 3, 64, 24), MM_F32, -1, 0, 24, MM_F32, -1),
+    "bcast": ((2, 3, 40, 64), MM_F32, -1, 0, (1, 1, 64, 24), MM_F32, -1, 0, 0, MM_F32, -1),
+    "bcast_rank": ((2, 3, 40, 64), MM_F32, -1, 0, (64, 24), MM_F32, -1, 0, 0, MM_F32, -1),
+    "bcast_a": ((1, 33, 50), MM_F32, -1, 0, (5, 50, 17), MM_F32, -1, 0, 0, MM_F32, -1),
+    "quantized": ((3, 33, 50), MM_U8, 31.5, 0, (3, 50, 17), MM_I8, 200.0, 0, 0, MM_F32, 1.0),
+    "quantized_u8": ((3, 33, 50), MM_U8, 31.5, 0, (3, 50, 17), MM_I8, 200.0, 0, 0, MM_U8, 0.0),
+    "mixed": ((3, 33, 50), MM_U8, 31.5, 0, (3, 50, 17), MM_F32, -1, 0, 0, MM_F32, -1),
+    "given_scales": ((2, 40, 64), MM_F32, 5.0, 0, (2, 64, 24), MM_F32, 3.0, 0, 0, MM_F32, -1),
+    "attention_qk": ((1, 2, 128, 64), MM_F32, -1, 0, (1, 2, 128, 64), MM_F32, -1, 1, 0, MM_F32, -1),
+    "attention_pv": ((1, 2, 128, 128), MM_F32, -1, 0, (1, 2, 128, 64), MM_F32, -1, 0, 0, MM_F32, -1),
+    "ragged": ((3, 7, 13), MM_F32, -1, 0, (3, 13, 5), MM_F32, -1, 0, 0, MM_F32, -1),
+}
+
+
+def matmul_inputs(name):
+    a_shape, a_dt, a_s, ta, b_shape, b_dt, b_s, tb, bias_n, c_dt, c_s = MATMUL_CASES[name]
+    seed = 8800 + sorted(MATMUL_CASES).index(name) * 3
+
+    def make(sd, shape, dt):
+        if dt == MM_F32:
+            return synth.normal(sd, shape)
+        return synth.u8(sd, shape) if dt == MM_U8 else synth.s8(sd, shape)
+
+    A, B = make(seed, a_shape, a_dt), make(seed + 1, b_shape, b_dt)
+    bias = synth.normal(seed + 2, (bias_n,)) if bias_n else None
+    return (A, a_dt, a_s, ta, B, b_dt, b_s, tb, bias, c_dt, c_s)

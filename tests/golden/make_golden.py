@@ -142,14 +142,26 @@ def bnn_outputs():
     return out
 
 
+def matmul_outputs():
+    """the reference's matmul operator (compute/tensor/src/matmul.cpp) on its x86 int8 branch"""
+    out = {}
+    for name in cases.MATMUL_CASES:
+        rc, C, scale = O.ref_matmul(*cases.matmul_inputs(name))
+        assert rc == 0, name
+        out[name] = C
+        out[name + "_scale"] = np.float32(scale)
+    return out
+
+
 def main():
+    np.savez_compressed(os.path.join(HERE, "matmul.npz"), **matmul_outputs())
     np.savez_compressed(os.path.join(HERE, "bnn.npz"), **bnn_outputs())
     np.savez_compressed(os.path.join(HERE, "gemv_row.npz"), **gemv_row_outputs())
     np.savez_compressed(os.path.join(HERE, "conv.npz"), **conv_outputs())
     np.savez_compressed(os.path.join(HERE, "gemm.npz"), **gemm_outputs())
     np.savez_compressed(os.path.join(HERE, "gemv.npz"), **gemv_outputs())
     np.savez_compressed(os.path.join(HERE, "quantize.npz"), **quant_outputs())
-    for f in ("gemm.npz", "gemv.npz", "gemv_row.npz", "quantize.npz", "conv.npz"):
+    for f in ("gemm.npz", "gemv.npz", "gemv_row.npz", "quantize.npz", "conv.npz", "matmul.npz"):
         print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
 
 

@@ -257,3 +257,27 @@ def test_ref_quantize_sweep():
                 O.ref.ref_quantize(n, O.DT_I32, ptr(a), dt, ptr(qr), ptr(sr), 0)
                 qp, sp = port_quant("i32" + name, a, dst, sc)
                 assert same_bits(qr, qp) and same_bits(sr, sp), (n, name, sc)
+
+
+def test_golden_matmul():
+    """The restatement of the matmul operator, built from the scalar primitives, against the reference's outputs."""
+    g = np.load(os.path.join(GOLD, "matmul.npz"))
+    for name in cases.MATMUL_CASES:
+        C, scale = O.port_matmul(*cases.matmul_inputs(name))
+        assert C.shape == g[name].shape and C.tobytes() == g[name].tobytes(), name
+        assert np.float32(scale).tobytes() == g[name + "_scale"].tobytes(), name
+
+
+@needs_ref
+def test_ref_matmul_sweep():
+    """small shapes around the kernels' edge sizes, fp32 and dynamically quantized outputs"""
+    F, U = O.DT_F32, O.DT_U8_Q
+    for m, k, n in itertools.product([1, 2, 17, 48], [3, 64, 100], [1, 16, 49]):
+        for ta, tb in ((0, 0), (1, 1)):
+            A = synth.normal(m * 100 + k, (2, k, m) if ta else (2, m, k))
+            B = synth.normal(n * 100 + k + 1, (2, n, k) if tb else (2, k, n))
+            for c_dt, c_scale in ((F, -1.0), (U, -1.0)):
+                args = (A, F, -1.0, ta, B, F, -1.0, tb, None, c_dt, c_scale)
+                rc, Cr, sr = O.ref_matmul(*args)
+                Cp, sp = O.port_matmul(*args)
+                assert rc == 0 and Cr.tobytes() == Cp.tobytes() and np.float32(sr) == np.float32(sp), (m, k, n, ta, tb, c_dt)
