@@ -74,6 +74,42 @@ EE shim_conv_output_size(const TensorDesc *inDesc, const TensorDesc *fDesc,
     return ret;
 }
 
+// matmul as inference/engine/include/cpu/matmul_cpu.hpp drives it: output size, tmp bytes, run; scales in the tensors
+EE shim_matmul(const TensorDesc *aDesc, void *A, F32 aScale, int transposeA, const TensorDesc *bDesc, void *B,
+    F32 bScale, int transposeB, U32 biasLen, void *bias, DataType cType, F32 *cScale, void *C, TensorDesc *cDesc,
+    void *tmp, U32 tmpCapacity)
+{
+    ArchInfo a = b200();
+    Tensor ta = over(*aDesc, A), tb = over(*bDesc, B), tc;
+    ta.set_scale(aScale);
+    tb.set_scale(bScale);
+    EE ret = matmul_infer_output_size(&ta, transposeA != 0, &tb, transposeB != 0, &tc, &a);
+    if (ret != SUCCESS) {
+        return ret;
+    }
+    TensorDesc cd = tc.get_desc();
+    cd.dt = cType;
+    tc = over(cd, C);
+    tc.set_scale(*cScale);
+    U32 bytes = 0;
+    ret = matmul_infer_forward_tmp_bytes(ta, transposeA != 0, tb, transposeB != 0, tc, &bytes, &a);
+    if (ret != SUCCESS) {
+        return ret;
+    }
+    if (bytes > tmpCapacity) {
+        return NOT_MATCH;
+    }
+    std::vector<Tensor> tmps = {over(tensor1d(DT_U8, bytes), tmp)};
+    Tensor tbias;
+    if (biasLen > 0) {
+        tbias = over(tensor1d(DT_F32, biasLen), bias);
+    }
+    ret = matmul(ta, transposeA != 0, tb, transposeB != 0, tbias, tmps, tc, &a);
+    *cScale = tc.get_scale();
+    *cDesc = cd;
+    return ret;
+}
+
 // the sequence an operator runs once (algorithm, packed-filter size, packing) ...
 EE shim_conv_prepare(const TensorDesc *inDesc, const TensorDesc *fDesc, void *filter,
     const TensorDesc *outDesc, const ConvolutionParamSpec *p, const ActivationParamSpec *act,

@@ -9,7 +9,7 @@ committed) -- and compiles the copies with only -D_USE_CUDA_B200, so that the re
 integration/_build/libbolt_dispatch_b200.so, contains Bolt's public entry points
 
     matrix_matrix_multiply*, matrix_vector_multiply*                  (compute/blas_enhance/src/mmm.cpp, mvm.cpp)
-    quantize, dequantize, convolution*                                (compute/tensor/src/*.cpp)
+    quantize, dequantize, convolution*, matmul*                       (compute/tensor/src/*.cpp)
 
 with the new architecture as their only back end.  bolt_api_shim.cpp adds C-callable wrappers around the C++
 (Tensor-based) ones for the tests.  The edits are anchored on lines of the reference; if the reference
@@ -145,6 +145,26 @@ def patch_convolution(t):
     return t
 
 
+def patch_matmul(t):
+    t = _edit(t, '#include "blas_enhance.h"\n', B200_INCLUDE, "after")
+    # tmp bytes
+    t = _edit(t, "    bool quantA = false;\n    bool quantB = false;\n    bool quantC = false;\n",
+              "#ifdef _USE_CUDA_B200\n    if (IS_CUDA_B200(archInfo->arch)) {\n"
+              "        return matmul_infer_forward_tmp_bytes_cuda_b200(&matrixADesc, transposeA, &matrixBDesc, transposeB,\n"
+              "            &matrixCDesc, matrixCTensor.get_scale(), bytes);\n    }\n#endif\n")
+    # the operator: scales travel in the tensors
+    t = _edit(t, "    if (!isSameDataFormat(matrixADesc.df, DF_NCHW)) {\n        TensorDesc desc = matrixADesc;",
+              "#ifdef _USE_CUDA_B200\n    if (IS_CUDA_B200(arch)) {\n"
+              "        F32 cScale = matrixCTensor.get_scale();\n"
+              "        TensorDesc biasDesc = biasTensor.get_desc();\n"
+              "        void *bias = biasTensor.bytes() > 0 ? get_ptr_from_tensor(biasTensor, arch) : nullptr;\n"
+              "        EE ret = matmul_cuda_b200(&matrixADesc, transposeA, matrixA, matrixATensor.get_scale(), &matrixBDesc,\n"
+              "            transposeB, matrixB, matrixBTensor.get_scale(), &biasDesc, bias, tmpBytes, tmp, &matrixCDesc, matrixC,\n"
+              "            &cScale);\n"
+              "        matrixCTensor.set_scale(cScale);\n        return ret;\n    }\n#endif\n")
+    return t
+
+
 FILES = [
     ("common/uni/include/sys.h", "include/sys.h", patch_sys_h),
     ("compute/blas_enhance/src/mmm.cpp", "mmm.cpp", patch_mmm),
@@ -152,6 +172,7 @@ FILES = [
     ("compute/tensor/src/quantize.cpp", "quantize.cpp", patch_quantize),
     ("compute/tensor/src/dequantize.cpp", "dequantize.cpp", patch_dequantize),
     ("compute/tensor/src/convolution.cpp", "convolution.cpp", patch_convolution),
+    ("compute/tensor/src/matmul.cpp", "matmul.cpp", patch_matmul),
 ]
 
 
@@ -169,8 +190,9 @@ def build(bolt_root):
     cmd = ["g++", "-O2", "-fPIC", "-std=c++11", "-include", "cstdint", "-w", "-D_USE_CUDA_B200", "-shared", "-o", LIB]
     for d in inc:
         cmd += ["-I", d]
-    cmd += [os.path.join(src, f) for f in ("mmm.cpp", "mvm.cpp", "quantize.cpp", "dequantize.cpp", "convolution.cpp")]
-    cmd += [os.path.join(HERE, "bolt_api_shim.cpp"), os.path.join(bolt_root, "common/uni/src/profiling.cpp")]
+    cmd += [os.path.join(src, f) for f in ("mmm.cpp", "mvm.cpp", "quantize.cpp", "dequantize.cpp", "convolution.cpp", "matmul.cpp")]
+    cmd += [os.path.join(HERE, "bolt_api_shim.cpp"), os.path.join(bolt_root, "common/uni/src/profiling.cpp"),
+            os.path.join(bolt_root, "common/uni/src/tensor_transpose.cpp")]
     cmd += ["-L", os.path.join(ROOT, "bolt_b200", "lib"), "-lbolt_b200", "-Wl,-rpath,$ORIGIN/../../bolt_b200/lib", "-Wl,--no-undefined"]
     subprocess.check_call(cmd)
     return LIB

@@ -53,6 +53,8 @@ def bolt():
                              C.c_int, f32p, C.POINTER(TD), vp, C.c_uint32, vp, C.POINTER(TD), vp,
                              C.POINTER(B.ActivationParamSpec)],
     }
+    sig["shim_matmul"] = [C.POINTER(TD), vp, C.c_float, C.c_int, C.POINTER(TD), vp, C.c_float, C.c_int, C.c_uint32, vp, C.c_int, f32p,
+                          vp, C.POINTER(TD), vp, C.c_uint32]
     for name, args in sig.items():
         f = getattr(L, name)
         f.argtypes, f.restype = args, C.c_int
@@ -297,3 +299,26 @@ def test_bolt_convolution_golden():
             elt = cases.conv_eltwise(i, g[key].size)
             got, sc = conv_through_bolt(L, shape, xin, w, bias, blk, out_u8, actm, cases.CONV_SCALES, eltwise=elt)
             assert got.tobytes() == g[key].tobytes(), key
+
+
+@pytest.mark.gpu
+def test_bolt_matmul_golden():
+    """tensor/src/matmul.cpp with ArchInfo.arch = CUDA_B200: output size, tmp bytes and the run through Bolt's own
+    functions, scales carried by the Tensors"""
+    L = bolt()
+    g = np.load(os.path.join(GOLD, "matmul.npz"))
+    for name in cases.MATMUL_CASES:
+        A, a_dt, a_s, ta, Bm, b_dt, b_s, tb, bias, c_dt, c_s = cases.matmul_inputs(name)
+        a_desc, b_desc = B.tensor_nd(a_dt, A.shape), B.tensor_nd(b_dt, Bm.shape)
+        d_a, d_b = to_dev(A), to_dev(Bm)
+        d_bias = None if bias is None else to_dev(bias)
+        n_out = g[name].size
+        d_c, d_tmp = dev_zeros(4 * n_out), dev_zeros(1 << 22)
+        cs, cd = C.c_float(c_s), TD()
+        ok(L.shim_matmul(C.byref(a_desc), dptr(d_a), a_s, ta, C.byref(b_desc), dptr(d_b), b_s, tb, 0 if bias is None else bias.size,
+                         None if bias is None else dptr(d_bias), c_dt, C.byref(cs), dptr(d_c), C.byref(cd), dptr(d_tmp), 1 << 22), name)
+        ok(B.lib().bolt_b200_synchronize(), "synchronize")
+        got = to_host(d_c, g[name].dtype, n_out)
+        assert tuple(reversed(list(cd.dims[: cd.nDims]))) == g[name].shape, name
+        assert got.tobytes() == g[name].tobytes(), name
+        assert np.float32(cs.value).tobytes() == g[name + "_scale"].tobytes(), name
