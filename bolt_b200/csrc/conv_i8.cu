@@ -757,11 +757,16 @@ EE launch_conv_tcgen05(const ConvGeom &g, const ConvLaunch &a, cudaStream_t st)
     // first among equals.  With stride 1 along W a row of TW pixels is TW*16 contiguous bytes; the (c16, w)
     // dimensions are then merged so that TMA moves one 16*TW-byte run per row instead of TW 16-byte ones (a
     // TMA box is at most 256 elements wide, hence TW <= 16 on that path).
+    // A tile whose pixel count is a multiple of 8 lets one TMA request bring all 8 channel groups of a
+    // 128-byte K block (the groups then lie 128-byte aligned behind one another in shared memory); any other
+    // count needs a request per group, eight times as many.  So such shapes are preferred even when they
+    // overhang the image (TW may exceed OW by up to 7 columns: the overhang reads zeros and is not stored).
     const bool merged_w = (sW == 1);
     uint64_t best_tiles = ~0ull;
     uint32_t btw = 0, bth = 0, btn = 0;
     const uint32_t tw_max = merged_w ? 16u : 128u;
-    for (uint32_t tw = (OW < tw_max ? OW : tw_max); tw >= 1; --tw) {
+    const uint32_t ow8 = (uint32_t)B200_ALIGN(OW, 8);
+    for (uint32_t tw = (ow8 < tw_max ? ow8 : tw_max); tw >= 1; --tw) {
         if (tw * sW > 256) {
             continue;
         }
@@ -774,7 +779,10 @@ EE launch_conv_tcgen05(const ConvGeom &g, const ConvLaunch &a, cudaStream_t st)
             if (tn == 0) {
                 continue;
             }
-            const uint64_t tiles = (uint64_t)((OW + tw - 1) / tw) * ((OH + th - 1) / th) * ((N + tn - 1) / tn);
+            uint64_t tiles = (uint64_t)((OW + tw - 1) / tw) * ((OH + th - 1) / th) * ((N + tn - 1) / tn);
+            if ((tw * th * tn) % 8 != 0) {
+                tiles *= 4;  // weight of the eightfold request count
+            }
             if (tiles < best_tiles) {
                 best_tiles = tiles;
                 btw = tw;

@@ -246,6 +246,7 @@ def resnet_conv(peaks, batch=64, iters=5, out_u8=False):
     torch = _torch()
     L, tm = lib(), Timer()
     rows, tot_ops, tot_ms, tot_roof = [], 0.0, 0.0, 0.0
+    calls, keep = [], []
     peak_tensor = 2.0 * peaks["bf16_tflops"]   # TOP/s: no int8 entry in the measured peaks, 2 x the bf16 burst figure
     target = DT_U8_Q if out_u8 else DT_F32
     for (ic, hw, oc, k, st, pad) in RESNET50_LAYERS:
@@ -267,14 +268,16 @@ def resnet_conv(peaks, batch=64, iters=5, out_u8=False):
         known_out_scale = 9.5 if out_u8 else None      # u8 output: known output scale, fused requantization
         L.bolt_b200_set_pointer_mode(1)
 
-        def call():
+        def call(in_desc=in_desc, x=x, ftm_desc=ftm_desc, ftm=ftm, p=p, alg=alg, sc=sc, bias=bias, tb=tb, tmp=tmp,
+                 out_desc=out_desc, out=out):
             convolution(in_desc, _p(x), ftm_desc, _p(ftm), p, alg, list(sc), _p(bias), tb, _p(tmp), out_desc, _p(out), True,
                         None, known_out_scale)
 
-        fn = call
         fn = tm.graph(call)  # neither path leaves the stream: replay as a CUDA graph (no host time inside)
         ms = tm.run(fn, iters)
         L.bolt_b200_set_pointer_mode(0)
+        calls.append(call)
+        keep.append((w, ftm, x, tmp, out, bias))
         ops = 2.0 * batch * oc * oh * oh * ic * k * k
         # algorithmic bytes: input + filter + output once
         nbytes = batch * ic * hw * hw + oc * ic * k * k + batch * oc * oh * oh * (1 if out_u8 else 4)
@@ -287,10 +290,22 @@ def resnet_conv(peaks, batch=64, iters=5, out_u8=False):
         tot_ops += ops
         tot_ms += ms
         tot_roof += roof_ms
-        del w, ftm, x, tmp, out
-        torch.cuda.empty_cache()
+    # all 22 layers one after the other as one graph (each on its own buffers, 256 MiB evicted before every pass):
+    # what a network pass costs, without the front-end latency that a graph of a single short kernel shows
+    L.bolt_b200_set_pointer_mode(1)
+
+    def one_pass():
+        for c in calls:
+            c()
+
+    pass_ms = tm.run(tm.graph(one_pass), iters)
+    L.bolt_b200_set_pointer_mode(0)
+    del keep[:]
+    torch.cuda.empty_cache()
     return {"workload": "resnet50_int8_conv batch %d (%s out)" % (batch, "u8" if out_u8 else "fp32"), "rows": rows,
             "total_ms": tot_ms, "tops": tot_ops / tot_ms / 1e9, "roof_total_ms": tot_roof, "frac_of_roof": tot_roof / tot_ms,
+            "pass_ms": pass_ms, "pass_tops": tot_ops / pass_ms / 1e9, "pass_frac_of_roof": tot_roof / pass_ms,
+            "pass": "the 22 layers back to back in one CUDA graph; rows[] are single-layer graphs timed one at a time",
             "roof": "per layer max(ops / (2 x bf16_tflops), algorithmic bytes / hbm_gbs); `bound` names the binding one"}
 
 
