@@ -56,7 +56,7 @@ struct WeightTwin {
 
 // kernel families whose dynamic shared-memory limit has to be raised above 48 KiB; the attribute
 // belongs to the device that is current when it is set, so it is remembered per device context
-enum KernelFamily { KF_GEMM = 0, KF_CONV, KF_GEMV, KF_GEMV_ROW, KF_BNN, KF_PROBE, KF_COUNT };
+enum KernelFamily { KF_GEMM = 0, KF_CONV, KF_CONV_HALF, KF_GEMV, KF_GEMV_ROW, KF_BNN, KF_PROBE, KF_COUNT };
 
 struct DeviceCtx {
     int device = 0;

@@ -40,31 +40,47 @@ namespace {
 using namespace tc;
 
 constexpr int MAX_BLOCK_N = 256;
-constexpr int STAGES = 4;
 constexpr int EPI_WARPS = 8;
 constexpr int EPI_THREADS = EPI_WARPS * 32;
 constexpr int NUM_THREADS = 64 + EPI_THREADS;
-constexpr uint32_t TMEM_COLS = 512;
 constexpr int SMEM_A_STAGE = BLOCK_M * BLOCK_K;      // 8 K-chunks x 128 pixels x 16 B
-constexpr int SMEM_B_STAGE = MAX_BLOCK_N * BLOCK_K;
 constexpr int MAX_CLASSES = 16;                      // border classes of a layer (3 x 3 pad 1: 9)
 constexpr int MAX_AXIS_CLASSES = 8;
-constexpr int CLASS_PITCH = MAX_BLOCK_N + 4;         // int32 per class row; +4 staggers the banks of different classes
 
+// Two configurations of the kernel.  NB = 256: column blocks of up to 256 channels, four pipeline stages, all of
+// tensor memory and shared memory -- one CTA per SM.  NB = 128: column blocks of up to 128 channels, three
+// stages, half of tensor memory and less than half of shared memory, so that two CTAs share an SM: the layers
+// with few input channels or few pixels spend their time in latencies (first load, tensor-memory read, stores)
+// that a second resident CTA covers.
+template <int NB>
+struct Cfg {
+    static constexpr int MAX_N = NB;
+    static constexpr int STAGES = NB == 256 ? 4 : 3;
+    static constexpr uint32_t TMEM_COLS = 2 * NB;        // two accumulators
+    static constexpr int SMEM_B_STAGE = NB * BLOCK_K;
+    static constexpr int CLASS_PITCH = NB + 4;           // int32 per class row; +4 staggers the banks of different classes
+    static constexpr int CTAS_PER_SM = NB == 256 ? 1 : 2;
+};
+
+template <int NB>
 struct __align__(16) SmemCtl {
-    uint64_t full[STAGES];
-    uint64_t empty[STAGES];
+    uint64_t full[Cfg<NB>::STAGES];
+    uint64_t empty[Cfg<NB>::STAGES];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
     // constants of the column block being worked on: per border class the offset of every channel
     // (offsetC-like term + round(bias * scaleO)), and the conversion factor of every channel
-    __align__(16) int32_t offs[MAX_CLASSES * CLASS_PITCH];
-    __align__(16) float colf[MAX_BLOCK_N];
+    __align__(16) int32_t offs[MAX_CLASSES * Cfg<NB>::CLASS_PITCH];
+    __align__(16) float colf[NB];
 };
 
-constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * (SMEM_A_STAGE + SMEM_B_STAGE) + sizeof(SmemCtl);
+template <int NB>
+constexpr size_t smem_bytes()
+{
+    return 1024 + (size_t)Cfg<NB>::STAGES * (SMEM_A_STAGE + Cfg<NB>::SMEM_B_STAGE) + sizeof(SmemCtl<NB>);
+}
 
 struct ConvParams {
     uint32_t N, OH, OW, OC;
@@ -170,16 +186,17 @@ __device__ __forceinline__ void store_block16(const ConvParams &p, const int32_t
     }
 }
 
-template <int KIND>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+template <int KIND, int NB>
+__global__ void __launch_bounds__(NUM_THREADS, Cfg<NB>::CTAS_PER_SM)
 conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
     const __grid_constant__ ConvParams p)
 {
+    using CF = Cfg<NB>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *smem_a = smem;
-    uint8_t *smem_b = smem + STAGES * SMEM_A_STAGE;
-    SmemCtl *ctl = reinterpret_cast<SmemCtl *>(smem + STAGES * (SMEM_A_STAGE + SMEM_B_STAGE));
+    uint8_t *smem_b = smem + CF::STAGES * SMEM_A_STAGE;
+    SmemCtl<NB> *ctl = reinterpret_cast<SmemCtl<NB> *>(smem + CF::STAGES * (SMEM_A_STAGE + CF::SMEM_B_STAGE));
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
@@ -192,7 +209,7 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     if (threadIdx.x == 0) {
         prefetch_tensormap(&map_x);
         prefetch_tensormap(&map_w);
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < CF::STAGES; ++s) {
             mbar_init(&ctl->full[s], 1);
             mbar_init(&ctl->empty[s], 1);
         }
@@ -206,7 +223,7 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                          smem_u32(&ctl->tmem_base)),
-                     "r"(TMEM_COLS)
+                     "r"(CF::TMEM_COLS)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -259,8 +276,8 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                             tma_load_5d(&map_x, &ctl->full[stage], dst, 0, x, y, (int)n, (int)cb);
                         }
                     }
-                    tma_load_2d(&map_w, &ctl->full[stage], smem_b + stage * SMEM_B_STAGE, (int)(kb * BLOCK_K), (int)n0);
-                    if (++stage == STAGES) {
+                    tma_load_2d(&map_w, &ctl->full[stage], smem_b + stage * CF::SMEM_B_STAGE, (int)(kb * BLOCK_K), (int)n0);
+                    if (++stage == CF::STAGES) {
                         stage = 0;
                         phase ^= 1;
                     }
@@ -287,7 +304,7 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                     break;
                 }
                 tcgen05_fence_after();
-                const uint32_t tmem_d = tmem_base + acc * MAX_BLOCK_N;
+                const uint32_t tmem_d = tmem_base + acc * CF::MAX_N;
                 for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
                     if (!mbar_wait(&ctl->full[stage], phase)) {
                         ok = false;
@@ -296,7 +313,7 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                     tcgen05_fence_after();
                     const uint32_t nq = min(8u, p.total_chunks - kb * 8);
                     const uint32_t a_addr = smem_u32(smem_a + stage * SMEM_A_STAGE);
-                    const uint64_t db = make_desc_sw128(smem_u32(smem_b + stage * SMEM_B_STAGE));
+                    const uint64_t db = make_desc_sw128(smem_u32(smem_b + stage * CF::SMEM_B_STAGE));
                     for (uint32_t k = 0; 2 * k < nq; ++k) {
                         // A: two 16-byte K chunks per MMA, chunk_stride apart; 8-pixel groups 128 B apart.  Rows
                         // beyond the tile's pixels read the next chunk's bytes: their accumulators are never
@@ -305,7 +322,7 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                         umma_i8(tmem_d, da, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
                     }
                     tcgen05_commit(&ctl->empty[stage]);
-                    if (++stage == STAGES) {
+                    if (++stage == CF::STAGES) {
                         stage = 0;
                         phase ^= 1;
                     }
@@ -377,7 +394,7 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                                 v = -128 * sum;
                             }
                         }
-                        ctl->offs[cls * CLASS_PITCH + j] = v + boff;
+                        ctl->offs[cls * CF::CLASS_PITCH + j] = v + boff;
                     }
                 }
                 asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
@@ -414,8 +431,8 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             if (row_ok && n_classes > 1) {
                 cls = (uint32_t)p.row_class[oh] * p.n_cc + p.col_class[ow];
             }
-            const int32_t *offs_px = ctl->offs + cls * CLASS_PITCH;
-            const uint32_t tbase = tmem_base + ((quad * 32u) << 16) + acc * MAX_BLOCK_N;
+            const int32_t *offs_px = ctl->offs + cls * CF::CLASS_PITCH;
+            const uint32_t tbase = tmem_base + ((quad * 32u) << 16) + acc * CF::MAX_N;
             auto release = [&]() {
                 tcgen05_fence_before();
                 __syncwarp();
@@ -439,6 +456,23 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             };
             // two register buffers: the next chunk is on its way from tensor memory while this one is
             // converted and stored; the accumulator is released as soon as its last chunk has arrived
+            if (NB != 256) {
+                // two CTAs per SM: the other CTA's warps cover the read latency, and the register budget of
+                // a half SM leaves room for one buffer only
+                uint32_t ra[32];
+                for (uint32_t c = c_begin; c < c_end; ++c) {
+                    tmem_ld32(tbase + c * 32, ra);
+                    tmem_ld_wait(ra);
+                    if (c + 1 == c_end) {
+                        release();
+                    }
+                    emit(c, ra);
+                }
+                if (c_begin >= c_end) {
+                    release();
+                }
+                continue;
+            }
             uint32_t ra[32], rb[32];
             if (c_begin < c_end) {
                 tmem_ld32(tbase + c_begin * 32, ra);
@@ -477,7 +511,7 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     }
     if (warp == 1) {
         tcgen05_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(CF::TMEM_COLS)
                      : "memory");
     }
 }
@@ -590,11 +624,11 @@ bool get4d(const TensorDesc *d, Conv4d *o)
     return true;
 }
 
-uint32_t pick_conv_block_n(uint32_t tiles_m, uint32_t OC, int sms)
+uint32_t pick_conv_block_n(uint32_t tiles_m, uint32_t OC, int sms, uint32_t max_bn = 256)
 {
     uint32_t best = 32;
     double best_cost = 1e30;
-    for (uint32_t bn = 256; bn >= 32; bn -= 32) {
+    for (uint32_t bn = max_bn; bn >= 32; bn -= 32) {
         if (bn > B200_ALIGN(OC, 32) && bn != 32) {
             continue;
         }
@@ -607,6 +641,17 @@ uint32_t pick_conv_block_n(uint32_t tiles_m, uint32_t OC, int sms)
         }
     }
     return best;
+}
+
+// Two CTAs per SM pay where a tile is short and narrow: at most 64 output channels, or at most 128 behind a K
+// of one or two blocks.  Measured on the 22 ResNet-50-shaped layers at batch 64 (u8 output): 3x3 64->64 @56
+// 38.9 -> 28.3 us, 1x1 256->128 @56 28.7 -> 25.0 us, 1x1 64->64 and 256->64 @56 22.5 -> 20.5 us; wider or longer
+// layers lose (3x3 512->512 @14 s2 32.8 -> 51.2 us), the 256-wide tile reads the activations half as often.
+bool conv_prefers_half(uint32_t tiles_m, uint32_t OC, uint32_t num_kb, int sms)
+{
+    (void)tiles_m;
+    (void)sms;
+    return OC <= 64 || (OC <= 128 && num_kb <= 2);
 }
 
 struct ConvGeom {
@@ -717,9 +762,12 @@ EE launch_conv_tcgen05(const ConvGeom &g, const ConvLaunch &a, cudaStream_t st)
         return UNKNOWN;
     }
     {
-        const void *ks[3] = {(const void *)conv_u8s8_tcgen05_kernel<0>, (const void *)conv_u8s8_tcgen05_kernel<1>,
-            (const void *)conv_u8s8_tcgen05_kernel<2>};
-        B200_EE(raise_smem_limit(c, KF_CONV, ks, 3, SMEM_BYTES));
+        const void *ks[3] = {(const void *)conv_u8s8_tcgen05_kernel<0, 256>, (const void *)conv_u8s8_tcgen05_kernel<1, 256>,
+            (const void *)conv_u8s8_tcgen05_kernel<2, 256>};
+        B200_EE(raise_smem_limit(c, KF_CONV, ks, 3, smem_bytes<256>()));
+        const void *kh[3] = {(const void *)conv_u8s8_tcgen05_kernel<0, 128>, (const void *)conv_u8s8_tcgen05_kernel<1, 128>,
+            (const void *)conv_u8s8_tcgen05_kernel<2, 128>};
+        B200_EE(raise_smem_limit(c, KF_CONV_HALF, kh, 3, smem_bytes<128>()));
     }
     if (!tensor_map_encoder_available()) {
         return NOT_SUPPORTED;
@@ -821,7 +869,13 @@ EE launch_conv_tcgen05(const ConvGeom &g, const ConvLaunch &a, cudaStream_t st)
     p.total_chunks = FH * FW * g.ICb;
     p.num_kb = (p.total_chunks + 7) / 8;
     p.tiles_m = p.tiles_n_img * p.tiles_w * p.tiles_h;
-    p.block_n = pick_conv_block_n(p.tiles_m, OC, c->sm_count);
+    // which configuration: two CTAs per SM with column blocks of at most 128 channels, or one with up to 256
+    static const int force_half = [] {
+        const char *e = getenv("BOLT_B200_CONV_HALF");
+        return (e == nullptr || e[0] == '\0') ? -1 : atoi(e);
+    }();
+    const bool half_cfg = force_half >= 0 ? force_half != 0 : conv_prefers_half(p.tiles_m, OC, p.num_kb, c->sm_count);
+    p.block_n = half_cfg ? pick_conv_block_n(p.tiles_m, OC, 2 * c->sm_count, 128) : pick_conv_block_n(p.tiles_m, OC, c->sm_count);
     p.tiles_n = (OC + p.block_n - 1) / p.block_n;
     p.out = a.out;
     p.eltwise = a.eltwise;
@@ -866,13 +920,22 @@ EE launch_conv_tcgen05(const ConvGeom &g, const ConvLaunch &a, cudaStream_t st)
         }
     }
     const uint64_t tiles = (uint64_t)p.tiles_m * p.tiles_n;
-    const uint32_t grid = (uint32_t)(tiles < (uint64_t)c->sm_count ? tiles : (uint64_t)c->sm_count);
-    if (a.out_kind == 2) {
-        conv_u8s8_tcgen05_kernel<2><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_x, map_w, p);
+    const uint64_t slots = (uint64_t)c->sm_count * (half_cfg ? 2 : 1);
+    const uint32_t grid = (uint32_t)(tiles < slots ? tiles : slots);
+    if (half_cfg) {
+        if (a.out_kind == 2) {
+            conv_u8s8_tcgen05_kernel<2, 128><<<grid, NUM_THREADS, smem_bytes<128>(), st>>>(map_x, map_w, p);
+        } else if (a.out_kind == 1) {
+            conv_u8s8_tcgen05_kernel<1, 128><<<grid, NUM_THREADS, smem_bytes<128>(), st>>>(map_x, map_w, p);
+        } else {
+            conv_u8s8_tcgen05_kernel<0, 128><<<grid, NUM_THREADS, smem_bytes<128>(), st>>>(map_x, map_w, p);
+        }
+    } else if (a.out_kind == 2) {
+        conv_u8s8_tcgen05_kernel<2, 256><<<grid, NUM_THREADS, smem_bytes<256>(), st>>>(map_x, map_w, p);
     } else if (a.out_kind == 1) {
-        conv_u8s8_tcgen05_kernel<1><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_x, map_w, p);
+        conv_u8s8_tcgen05_kernel<1, 256><<<grid, NUM_THREADS, smem_bytes<256>(), st>>>(map_x, map_w, p);
     } else {
-        conv_u8s8_tcgen05_kernel<0><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_x, map_w, p);
+        conv_u8s8_tcgen05_kernel<0, 256><<<grid, NUM_THREADS, smem_bytes<256>(), st>>>(map_x, map_w, p);
     }
     count_launch();
     B200_CUDA(cudaGetLastError());

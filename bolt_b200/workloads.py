@@ -240,9 +240,10 @@ RESNET50_LAYERS = [
     (512, 7, 512, 3, 1, 1), (512, 7, 2048, 1, 1, 0), (2048, 7, 512, 1, 1, 0)]
 
 
-def resnet_conv(peaks, batch=64, iters=5, out_u8=False):
+def resnet_conv(peaks, batch=64, iters=5, out_u8=False, once=False):
     """int8 convolution, NCHWc16 u8 input, fused bias + ReLU; fp32 output, or u8 output requantized in
-    the epilogue with a known output scale."""
+    the epilogue with a known output scale.  once: every layer is launched a single time and nothing is timed
+    (one launch per layer for a profiler to capture)."""
     torch = _torch()
     L, tm = lib(), Timer()
     rows, tot_ops, tot_ms, tot_roof = [], 0.0, 0.0, 0.0
@@ -273,6 +274,13 @@ def resnet_conv(peaks, batch=64, iters=5, out_u8=False):
             convolution(in_desc, _p(x), ftm_desc, _p(ftm), p, alg, list(sc), _p(bias), tb, _p(tmp), out_desc, _p(out), True,
                         None, known_out_scale)
 
+        if once:
+            tm.evict()
+            call()
+            torch.cuda.synchronize()
+            L.bolt_b200_set_pointer_mode(0)
+            rows.append({"layer": "%dx%d %d->%d @%d s%d" % (k, k, ic, oc, hw, st)})
+            continue
         fn = tm.graph(call)  # neither path leaves the stream: replay as a CUDA graph (no host time inside)
         ms = tm.run(fn, iters)
         L.bolt_b200_set_pointer_mode(0)
@@ -290,6 +298,9 @@ def resnet_conv(peaks, batch=64, iters=5, out_u8=False):
         tot_ops += ops
         tot_ms += ms
         tot_roof += roof_ms
+    if once:
+        return {"workload": "resnet50_int8_conv batch %d (%s out), one launch per layer" % (batch, "u8" if out_u8 else "fp32"),
+                "rows": rows}
     # all 22 layers one after the other as one graph (each on its own buffers, 256 MiB evicted before every pass):
     # what a network pass costs, without the front-end latency that a graph of a single short kernel shows
     L.bolt_b200_set_pointer_mode(1)
@@ -341,9 +352,13 @@ def bnn(peaks, batch=128, iters=5):
             "note": "bound by the popcount rate (16 per clock per SM, 4.45 T/s measured), not by HBM"}
 
 
+def resnet_conv_u8_once(peaks):
+    return resnet_conv(peaks, out_u8=True, once=True)
+
+
 def resnet_conv_u8(peaks):
     return resnet_conv(peaks, out_u8=True)
 
 
-WORKLOADS = {"ffn": ffn_sweep, "gemv": gemv, "quantize": quantize, "resnet_conv": resnet_conv,
+WORKLOADS = {"ffn": ffn_sweep, "gemv": gemv, "quantize": quantize, "resnet_conv": resnet_conv, "resnet_conv_u8_once": resnet_conv_u8_once,
              "resnet_conv_u8": resnet_conv_u8, "bnn": bnn, "i8_peak": i8_peak}
