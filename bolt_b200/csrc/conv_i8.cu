@@ -121,21 +121,37 @@ __device__ __forceinline__ void store_block16(const ConvParams &p, const int32_t
     if (KIND == 2) {
         uint8_t *out = reinterpret_cast<uint8_t *>(p.out) + base;
         uint32_t w[4];
+        // Adding 1.5 * 2^23 rounds f to an integer (nearest even) in the low mantissa bits: the word is
+        // 0x4B400000 + rne(f), and while 0 <= rne(f) <= 255 its low byte is the result.  `seen` collects the
+        // other bits of all 16 words; anything left there (rare: the output scale does not fit the data)
+        // sends the block through the clamp -- negatives wrap above 255 like vpmovusdb reads them.
+        const int floor_v = p.relu ? 0 : (int)0x80000000;
+        uint32_t bits[16];
+        uint32_t seen = 0;
 #pragma unroll
         for (int j = 0; j < 16; j += 4) {
             const int4 o = *reinterpret_cast<const int4 *>(offs + j);
             const float4 c4 = *reinterpret_cast<const float4 *>(colf + j);
             const float cf[4] = {c4.x, c4.y, c4.z, c4.w};
-            int v[4] = {(int)r[j] + o.x, (int)r[j + 1] + o.y, (int)r[j + 2] + o.z, (int)r[j + 3] + o.w};
-            uint32_t b[4];
+            const int v[4] = {(int)r[j] + o.x, (int)r[j + 1] + o.y, (int)r[j + 2] + o.z, (int)r[j + 3] + o.w};
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
-                const int a = p.relu ? max(v[t], 0) : v[t];
-                const float f = __fadd_rn(__fmul_rn(__int2float_rn(a), cf[t]), 128.0f);
-                // rne(f) as unsigned, clamped at 255: negatives wrap above 255 like vpmovusdb reads them
-                b[t] = min(__float_as_uint(__fadd_rn(f, 12582912.0f)) - 0x4B400000u, 255u);
+                const float f = __fadd_rn(__fmul_rn(__int2float_rn(max(v[t], floor_v)), cf[t]), 128.0f);
+                bits[j + t] = __float_as_uint(__fadd_rn(f, 12582912.0f));
+                seen |= bits[j + t] ^ 0x4B400000u;
             }
-            w[j >> 2] = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+            w[j >> 2] = __byte_perm(__byte_perm(bits[j], bits[j + 1], 0x0040), __byte_perm(bits[j + 2], bits[j + 3], 0x0040), 0x5410);
+        }
+        if (seen > 255u) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 4) {
+                uint32_t b[4];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    b[t] = min(bits[j + t] - 0x4B400000u, 255u);
+                }
+                w[j >> 2] = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+            }
         }
         if (width == 16) {
             *reinterpret_cast<uint4 *>(out) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -350,6 +366,13 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         const uint32_t c_end = half ? nch : ((nch + 1) >> 1);
         uint32_t staged_n0 = 0xFFFFFFFFu;
         uint32_t it = 0;
+        // this lane's pixel inside a tile (the same for every tile): image, row and column offsets
+        const uint32_t px_r = quad * 32 + lane;
+        const uint32_t px_per_img = p.TH * p.TW;
+        const uint32_t px_nl = px_r / px_per_img;
+        const uint32_t px_rem = px_r - px_nl * px_per_img;
+        const uint32_t px_th = px_rem / p.TW;
+        const uint32_t px_tw = px_rem - px_th * p.TW;
         // After a bounded wait ran out somewhere the warp keeps walking the tiles without touching them:
         // the named barriers below have to be reached by every epilogue warp the same number of times.
         bool dead = false;
@@ -416,15 +439,10 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             }
             tcgen05_fence_after();
             // this lane's pixel
-            const uint32_t r = quad * 32 + lane;
-            const uint32_t per_img = p.TH * p.TW;
-            const uint32_t nl = r / per_img;
-            const uint32_t rem = r - nl * per_img;
-            const uint32_t th = rem / p.TW;
-            const uint32_t oh = oh0 + th;
-            const uint32_t ow = ow0 + (rem - th * p.TW);
-            const uint32_t n = n_first + nl;
-            const bool row_ok = r < p.rows && n < p.N && oh < p.OH && ow < p.OW;
+            const uint32_t oh = oh0 + px_th;
+            const uint32_t ow = ow0 + px_tw;
+            const uint32_t n = n_first + px_nl;
+            const bool row_ok = px_r < p.rows && n < p.N && oh < p.OH && ow < p.OW;
             const size_t pix = (size_t)oh * p.OW + ow;
             const size_t plane = (size_t)p.OH * p.OW;
             uint32_t cls = 0;
