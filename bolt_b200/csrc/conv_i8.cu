@@ -222,6 +222,9 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     // count is not a multiple of 8 gets one load per chunk (G = 1) at a rounded-up distance
     const uint32_t chunk_stride = ((p.rows + 7u) & ~7u) * 16;
 
+    // programmatic dependent launch: the next kernel of the stream may begin its own set-up while this one runs;
+    // this kernel touches no global memory before griddepcontrol.wait (the previous kernel has then completed)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (threadIdx.x == 0) {
         prefetch_tensormap(&map_x);
         prefetch_tensormap(&map_w);
@@ -247,6 +250,7 @@ conv_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // tile -> (first image, patch origin, first output channel)
     auto decode = [&](uint32_t tile, uint32_t &n, uint32_t &oh0, uint32_t &ow0, uint32_t &n0) {
@@ -772,6 +776,42 @@ struct ConvLaunch {
     int out_kind, relu;
 };
 
+// Launch with programmatic stream serialization (the kernel's set-up overlaps the tail of the previous kernel);
+// if the attribute is refused outside a stream capture, launch without it from then on.
+std::atomic<int> g_conv_pdl{-1};
+template <int KIND, int NB>
+cudaError_t launch_conv_kernel(uint32_t grid, cudaStream_t st, const CUtensorMap &mx, const CUtensorMap &mw, const ConvParams &p)
+{
+    int pdl = g_conv_pdl.load(std::memory_order_relaxed);
+    if (pdl < 0) {
+        const char *e = getenv("BOLT_B200_NO_PDL");
+        pdl = (e != nullptr && e[0] != '\0' && e[0] != '0') ? 0 : 1;
+        g_conv_pdl.store(pdl, std::memory_order_relaxed);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = smem_bytes<NB>();
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, conv_u8s8_tcgen05_kernel<KIND, NB>, mx, mw, p);
+    if (e != cudaSuccess && pdl) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        cudaStreamIsCapturing(st, &cap);
+        if (cap == cudaStreamCaptureStatusNone) {
+            cudaGetLastError();
+            g_conv_pdl.store(0, std::memory_order_relaxed);
+            cfg.numAttrs = 0;
+            e = cudaLaunchKernelEx(&cfg, conv_u8s8_tcgen05_kernel<KIND, NB>, mx, mw, p);
+        }
+    }
+    return e;
+}
+
 // run the implicit-GEMM kernel (all pointers device)
 EE launch_conv_tcgen05(const ConvGeom &g, const ConvLaunch &a, cudaStream_t st)
 {
@@ -812,8 +852,16 @@ EE launch_conv_tcgen05(const ConvGeom &g, const ConvLaunch &a, cudaStream_t st)
     // 1x1, stride 1, nothing padded: every image is one row of H*W pixels
     if (FH == 1 && FW == 1 && sH == 1 && sW == 1 && p.n_rc == 1 && p.n_cc == 1 && a.pt == 0 && a.pl == 0 && OH == H &&
         OW == W) {
-        W = OW = H * W;
-        H = OH = 1;
+        // ... or, when the pixel count allows, rows of 16 pixels (256 contiguous bytes): a tile of 8 such rows is
+        // 128 consecutive pixels of ONE image, 2 KiB contiguous per channel group, instead of 16 pixels of each
+        // of 8 images -- longer runs per DRAM page when the input streams from HBM
+        if ((H * W) % 16 == 0) {
+            H = OH = H * W / 16;
+            W = OW = 16;
+        } else {
+            W = OW = H * W;
+            H = OH = 1;
+        }
     }
     p.N = N;
     p.OH = OH;
@@ -940,23 +988,18 @@ EE launch_conv_tcgen05(const ConvGeom &g, const ConvLaunch &a, cudaStream_t st)
     const uint64_t tiles = (uint64_t)p.tiles_m * p.tiles_n;
     const uint64_t slots = (uint64_t)c->sm_count * (half_cfg ? 2 : 1);
     const uint32_t grid = (uint32_t)(tiles < slots ? tiles : slots);
+    cudaError_t le;
     if (half_cfg) {
-        if (a.out_kind == 2) {
-            conv_u8s8_tcgen05_kernel<2, 128><<<grid, NUM_THREADS, smem_bytes<128>(), st>>>(map_x, map_w, p);
-        } else if (a.out_kind == 1) {
-            conv_u8s8_tcgen05_kernel<1, 128><<<grid, NUM_THREADS, smem_bytes<128>(), st>>>(map_x, map_w, p);
-        } else {
-            conv_u8s8_tcgen05_kernel<0, 128><<<grid, NUM_THREADS, smem_bytes<128>(), st>>>(map_x, map_w, p);
-        }
-    } else if (a.out_kind == 2) {
-        conv_u8s8_tcgen05_kernel<2, 256><<<grid, NUM_THREADS, smem_bytes<256>(), st>>>(map_x, map_w, p);
-    } else if (a.out_kind == 1) {
-        conv_u8s8_tcgen05_kernel<1, 256><<<grid, NUM_THREADS, smem_bytes<256>(), st>>>(map_x, map_w, p);
+        le = a.out_kind == 2 ? launch_conv_kernel<2, 128>(grid, st, map_x, map_w, p)
+                             : (a.out_kind == 1 ? launch_conv_kernel<1, 128>(grid, st, map_x, map_w, p)
+                                                : launch_conv_kernel<0, 128>(grid, st, map_x, map_w, p));
     } else {
-        conv_u8s8_tcgen05_kernel<0, 256><<<grid, NUM_THREADS, smem_bytes<256>(), st>>>(map_x, map_w, p);
+        le = a.out_kind == 2 ? launch_conv_kernel<2, 256>(grid, st, map_x, map_w, p)
+                             : (a.out_kind == 1 ? launch_conv_kernel<1, 256>(grid, st, map_x, map_w, p)
+                                                : launch_conv_kernel<0, 256>(grid, st, map_x, map_w, p));
     }
     count_launch();
-    B200_CUDA(cudaGetLastError());
+    B200_CUDA(le);
     return SUCCESS;
 }
 
