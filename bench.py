@@ -542,7 +542,7 @@ def main():
     ap.add_argument("--no-sharded", action="store_true", help="with --gpus > 1: skip the N-split FFN record")
     ap.add_argument("--workload", default="bert_stack",
                     help="bert_stack (the headline, default) or one of the side workloads: ffn, gemv, quantize, "
-                         "resnet_conv, resnet_conv_u8, bnn, i8_peak (1 GPU, prints that workload's figures as one "
+                         "resnet_conv, resnet_conv_u8, bnn, pooling, i8_peak (1 GPU, prints that workload's figures as one "
                          "JSON line with the clocks sampled while it ran)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -91,6 +91,17 @@ class ConvolutionParamSpec(C.Structure):
         (k, C.c_uint32) for k in ("round_mode", "output_pad_t", "output_pad_h", "output_pad_w")]
 
 
+class PoolingParamSpec(C.Structure):
+    """parameter_spec.h:285-301"""
+    _pack_ = 8
+    _fields_ = [(k, C.c_uint32) for k in ("kernel_t", "kernel_h", "kernel_w", "stride_t", "stride_h", "stride_w", "pad_before",
+                                          "pad_after", "pad_top", "pad_bottom", "pad_left", "pad_right", "round_mode", "mode")] + [
+        ("count_include_pad", C.c_bool)]
+
+
+POOLING_MAX, POOLING_MEAN = 0, 1
+
+
 class ConvExt(C.Structure):
     """bolt_b200_conv_ext"""
     _fields_ = [("output_scale", C.c_float), ("filter_scales", C.c_void_p)]
@@ -113,6 +124,7 @@ SIGNATURES = {
     "bolt_b200_use_para": (C.c_int, [_vp]),
     "bolt_b200_i8_mma_rate": (C.c_int, [C.c_uint32, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "bolt_b200_selftest_wait_limit": (C.c_int, [C.c_uint32]),
+    "pooling_cuda_b200": (C.c_int, [_TDp, _vp, C.POINTER(PoolingParamSpec), _vp, _TDp, _vp]),
     "matmul_infer_output_size_cuda_b200": (C.c_int, [_TDp, C.c_int, _TDp, C.c_int, _TDp]),
     "matmul_infer_forward_tmp_bytes_cuda_b200": (C.c_int, [_TDp, C.c_int, _TDp, C.c_int, _TDp, C.c_float, C.POINTER(C.c_uint32)]),
     "matmul_cuda_b200": (C.c_int, [_TDp, C.c_int, _vp, C.c_float, _TDp, C.c_int, _vp, C.c_float, _TDp, _vp, C.c_uint32, _vp,
@@ -276,6 +288,26 @@ def dequantize(qDesc, qData, scale, dDesc, dData):
     b = tensor1d(DT_F32, 0)
     CHECK_STATUS(lib().dequantize_cuda_b200(C.byref(qDesc), qData, C.cast(arr, _f32p), C.byref(b), None,
                                             C.byref(dDesc), dData), "dequantize")
+
+
+# ---- pooling (u8, NCHWc16) ------------------------------------------------------------------------------
+def pooling_param(kernel, stride, pad, mean=False, count_include_pad=False):
+    p = PoolingParamSpec()
+    p.kernel_t, p.kernel_h, p.kernel_w = 1, kernel, kernel
+    p.stride_t, p.stride_h, p.stride_w = 1, stride, stride
+    p.pad_top = p.pad_bottom = p.pad_left = p.pad_right = pad
+    p.round_mode = 0
+    p.mode = POOLING_MEAN if mean else POOLING_MAX
+    p.count_include_pad = bool(count_include_pad)
+    return p
+
+
+def pooling(inputDesc, input_ptr, p, scale, outputDesc, output_ptr):
+    """scale: list [input scale, output scale]; the output scale is written back"""
+    arr = (C.c_float * 2)(*scale)
+    CHECK_STATUS(lib().pooling_cuda_b200(C.byref(inputDesc), input_ptr, C.byref(p), C.cast(arr, _vp), C.byref(outputDesc), output_ptr),
+                 "pooling")
+    scale[0], scale[1] = arr[0], arr[1]
 
 
 # ---- matmul (compute/tensor/include/tensor_computing.h: matmul_infer_output_size, _tmp_bytes, matmul) -----

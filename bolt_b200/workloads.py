@@ -320,6 +320,34 @@ def resnet_conv(peaks, batch=64, iters=5, out_u8=False, once=False):
             "roof": "per layer max(ops / (2 x bf16_tflops), algorithmic bytes / hbm_gbs); `bound` names the binding one"}
 
 
+def pooling(peaks, iters=10):
+    """u8 pooling, NCHWc16: the 3x3 stride-2 maximum after a ResNet stem (64 x 112 x 112, batch 64: 51 MB in, 13 MB out)
+    and a 2x2 stride-2 mean on 256 x 56 x 56."""
+    from . import pooling as pool_call, pooling_param
+    torch = _torch()
+    L, tm = lib(), Timer()
+    rows = []
+    for name, (n, c, hw, k, s, pad, mean) in (("max 3x3 s2 p1 64x112x112 b64", (64, 64, 112, 3, 2, 1, False)),
+                                              ("mean 2x2 s2 256x56x56 b64", (64, 256, 56, 2, 2, 0, True))):
+        oh = (hw + 2 * pad - k) // s + 1
+        x = torch.randint(128, 256, (n * c * hw * hw,), dtype=torch.uint8, device="cuda")
+        y = torch.empty(n * c * oh * oh, dtype=torch.uint8, device="cuda")
+        in_desc = tensor4df(DT_U8_Q, DF_NCHWC16, n, c, hw, hw)
+        out_desc = tensor4df(DT_U8_Q, DF_NCHWC16, n, c, oh, oh)
+        pp = pooling_param(k, s, pad, mean)
+        L.bolt_b200_set_pointer_mode(1)
+
+        def call(in_desc=in_desc, x=x, pp=pp, out_desc=out_desc, y=y):
+            pool_call(in_desc, _p(x), pp, [1.0, 0.0], out_desc, _p(y))
+
+        ms = tm.run(tm.graph(call), iters)
+        L.bolt_b200_set_pointer_mode(0)
+        nbytes = x.numel() + y.numel()
+        rows.append({"case": name, "ms": ms, "GBps": nbytes / ms / 1e6, "frac_of_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"]})
+        del x, y
+    return {"workload": "u8 pooling NCHWc16 (algorithmic bytes: input + output once)", "rows": rows}
+
+
 def bnn(peaks, batch=128, iters=5):
     """1-bit 3x3 convolution, C 256 -> 256, 28 x 28, pad 1, XNOR mode, fp16 NCHWc8 in and out."""
     torch = _torch()
@@ -361,4 +389,4 @@ def resnet_conv_u8(peaks):
 
 
 WORKLOADS = {"ffn": ffn_sweep, "gemv": gemv, "quantize": quantize, "resnet_conv": resnet_conv, "resnet_conv_u8_once": resnet_conv_u8_once,
-             "resnet_conv_u8": resnet_conv_u8, "bnn": bnn, "i8_peak": i8_peak}
+             "resnet_conv_u8": resnet_conv_u8, "bnn": bnn, "i8_peak": i8_peak, "pooling": pooling}

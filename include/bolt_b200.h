@@ -25,6 +25,7 @@
 #ifndef BOLT_B200_H
 #define BOLT_B200_H
 
+#include <stdbool.h>
 #include <stddef.h>
 #include <stdint.h>
 
@@ -150,6 +151,16 @@ typedef struct {
     uint32_t round_mode;
     U32 output_pad_t, output_pad_h, output_pad_w;
 } ConvolutionParamSpec;
+typedef uint32_t PoolingMode;
+enum { POOLING_MAX = 0, POOLING_MEAN = 1 };
+typedef struct {
+    U32 kernel_t, kernel_h, kernel_w;
+    U32 stride_t, stride_h, stride_w;
+    U32 pad_before, pad_after, pad_top, pad_bottom, pad_left, pad_right;
+    uint32_t round_mode;
+    PoolingMode mode;
+    bool count_include_pad;
+} PoolingParamSpec; /* parameter_spec.h:285-301 */
 #pragma pack(pop)
 #endif /* BOLT_B200_WITH_BOLT_HEADERS */
 
@@ -399,6 +410,14 @@ EE bolt_b200_convolution_ex(const TensorDesc *inputDesc, void *input, void *eltw
     const TensorDesc *biasDesc, const void *bias, U32 tmpBytes, void *tmp,
     const TensorDesc *outputDesc, void *output, const ActivationParamSpec *activationDesc,
     const bolt_b200_conv_ext *ext);
+
+/* ---- pooling: the u8 branch of Bolt's operator (cpu/x86/pooling.cpp:50-55 -> int8/avx512/pooling_int8.cpp:317-429)
+ * U8_Q NCHWc16 in and out, maximum or mean over kernel_h x kernel_w windows clipped to the image.  scale, if not
+ * NULL, points at {input scale, output scale}: the output scale is written (pooling_int8.cpp:362-371).  The
+ * mean uses the reference's integer arithmetic, including its logical shift (a window below the zero point
+ * stores 255).  Replaces pooling_x86 for DT_U8_Q. */
+EE pooling_cuda_b200(const TensorDesc *inputDesc, const void *input, const PoolingParamSpec *poolingParamSpec,
+    void *scale, const TensorDesc *outputDesc, void *output);
 
 /* ---- matmul: the int8 branch of Bolt's operator (compute/tensor/src/matmul.cpp:303-557) ------------------
  * Both operands are activations: fp32 ones are quantized per call (A to U8_Q and B to I8; when the result

@@ -92,5 +92,20 @@ int main()
     V(offsetof(ConvolutionParamSpec, output_pad_t));
     V(offsetof(ConvolutionParamSpec, output_pad_h));
     V(offsetof(ConvolutionParamSpec, output_pad_w));
+    V(sizeof(PoolingMode));
+    V(POOLING_MAX);
+    V(POOLING_MEAN);
+    V(sizeof(PoolingParamSpec));
+    V(offsetof(PoolingParamSpec, kernel_t));
+    V(offsetof(PoolingParamSpec, kernel_h));
+    V(offsetof(PoolingParamSpec, kernel_w));
+    V(offsetof(PoolingParamSpec, stride_h));
+    V(offsetof(PoolingParamSpec, stride_w));
+    V(offsetof(PoolingParamSpec, pad_top));
+    V(offsetof(PoolingParamSpec, pad_left));
+    V(offsetof(PoolingParamSpec, pad_right));
+    V(offsetof(PoolingParamSpec, round_mode));
+    V(offsetof(PoolingParamSpec, mode));
+    V(offsetof(PoolingParamSpec, count_include_pad));
     return 0;
 }

@@ -95,6 +95,7 @@ def _load_port():
     lib.oracle_bias_offsetc.argtypes = [_vp, _vp, _u32, _c.c_float, _vp]
     lib.oracle_dequantize_i32_f32.argtypes = [_vp, _u64, _c.c_float, _vp]
     lib.oracle_dequantize_u8_f32.argtypes = [_vp, _u64, _c.c_float, _vp]
+    lib.oracle_pooling_u8.argtypes = [_u32] * 12 + [_i32, _i32, _vp, _vp, _vp]
     if hasattr(lib, "oracle_conv_int8"):
         lib.oracle_conv_out_hw.argtypes = [_c.POINTER(ConvShape), _vp, _vp]
         lib.oracle_conv_int8.argtypes = [_c.POINTER(ConvShape), _vp, _vp, _vp, _vp, _vp, _vp, _vp]

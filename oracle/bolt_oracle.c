@@ -337,6 +337,74 @@ void oracle_dequantize_u8_f32(const uint8_t *q, uint64_t n, float scale, float *
 }
 
 /* ------------------------------------------------------------------------------ */
+/* u8 pooling on NCHWc16 (compute/tensor/src/cpu/x86/int8/avx512/pooling_int8.cpp)  */
+/* ------------------------------------------------------------------------------ */
+
+/* pooling_uint8, :317-429.  mode 0 = max (vpmaxub over the clipped window), 1 = mean: the sum of the window
+ * minus 128 per element, times poolSize = 65536 / (KH*KW) -- or 65536 / (clipped size) when padding is not
+ * counted -- as a 32-bit product (vpmulld), LOGICAL shift right by 16 (vpsrld: a negative sum becomes a large
+ * word), plus 128, stored with unsigned saturation (vpmovusdb): :277-314.  scale[1] receives the output scale
+ * (:362-366).  Returns 0, or 51 (NOT_SUPPORTED) / 2 (NOT_MATCH) where the reference refuses. */
+int oracle_pooling_u8(uint32_t n, uint32_t c, uint32_t ih, uint32_t iw, uint32_t oh, uint32_t ow, uint32_t kh_, uint32_t kw_,
+    uint32_t sh, uint32_t sw, uint32_t pt, uint32_t pl, int mode, int count_include_pad, const uint8_t *in, uint8_t *out,
+    float *scale)
+{
+    if (pt >= kh_ || pl >= kw_) {
+        return 51;
+    }
+    if (c % 16 != 0) {
+        return 2;
+    }
+    const int32_t shift = 65536;
+    const int32_t factor = shift / (int32_t)(kh_ * kw_);
+    if (factor < 1 || (mode != 0 && mode != 1)) {
+        return 51;
+    }
+    if (scale != NULL) {
+        scale[1] = (mode == 0) ? scale[0] : scale[0] * factor * (kw_ * kh_) / (float)shift;
+    }
+    const uint32_t cb = c / 16;
+    for (uint32_t img = 0; img < n * cb; ++img) {
+        const uint8_t *src = in + (size_t)img * ih * iw * 16;
+        uint8_t *dst = out + (size_t)img * oh * ow * 16;
+        for (uint32_t h = 0; h < oh; ++h) {
+            for (uint32_t w = 0; w < ow; ++w) {
+                int hs = (int)(h * sh) - (int)pt, ws = (int)(w * sw) - (int)pl;
+                int he = hs + (int)kh_ < (int)ih ? hs + (int)kh_ : (int)ih;
+                int we = ws + (int)kw_ < (int)iw ? ws + (int)kw_ : (int)iw;
+                hs = hs > 0 ? hs : 0;
+                ws = ws > 0 ? ws : 0;
+                const int kh = he - hs, kw = we - ws;
+                const int32_t pool = count_include_pad ? factor : shift / (kh * kw);
+                for (int ch = 0; ch < 16; ++ch) {
+                    if (mode == 0) {
+                        uint8_t m = src[((size_t)hs * iw + ws) * 16 + ch];
+                        for (int y = hs; y < he; ++y) {
+                            for (int x = ws; x < we; ++x) {
+                                const uint8_t v = src[((size_t)y * iw + x) * 16 + ch];
+                                m = v > m ? v : m;
+                            }
+                        }
+                        dst[((size_t)h * ow + w) * 16 + ch] = m;
+                    } else {
+                        int32_t acc = -128 * kh * kw;
+                        for (int y = hs; y < he; ++y) {
+                            for (int x = ws; x < we; ++x) {
+                                acc += src[((size_t)y * iw + x) * 16 + ch];
+                            }
+                        }
+                        const uint32_t prod = (uint32_t)acc * (uint32_t)pool;   /* vpmulld: low 32 bits */
+                        const uint32_t v = (prod >> 16) + 128u;
+                        dst[((size_t)h * ow + w) * 16 + ch] = (uint8_t)(v > 255u ? 255u : v);
+                    }
+                }
+            }
+        }
+    }
+    return 0;
+}
+
+/* ------------------------------------------------------------------------------ */
 /* int8 convolution                                                               */
 /* ------------------------------------------------------------------------------ */
 

@@ -63,6 +63,9 @@ void oracle_bias_offsetc(const float *bias, const int32_t *offsetC, uint32_t n, 
     int32_t *out);
 void oracle_dequantize_i32_f32(const int32_t *q, uint64_t n, float scale, float *out);
 void oracle_dequantize_u8_f32(const uint8_t *q, uint64_t n, float scale, float *out);
+int oracle_pooling_u8(uint32_t n, uint32_t c, uint32_t ih, uint32_t iw, uint32_t oh, uint32_t ow, uint32_t kh, uint32_t kw,
+    uint32_t sh, uint32_t sw, uint32_t pt, uint32_t pl, int mode, int count_include_pad, const uint8_t *in, uint8_t *out,
+    float *scale);
 
 /* ---- int8 convolution ------------------------------------------------------------ */
 typedef struct {

@@ -321,4 +321,29 @@ void ref_conv_free(RefConvPlan *pl)
     }
 }
 
+
+// ---- u8 pooling (cpu/x86/int8/avx512/pooling_int8.cpp: pooling_uint8) --------------------------
+int ref_pooling_u8(uint32_t n, uint32_t c, uint32_t ih, uint32_t iw, uint32_t oh, uint32_t ow, uint32_t kh, uint32_t kw,
+    uint32_t sh, uint32_t sw, uint32_t pt, uint32_t pl, int mode, int count_include_pad, const uint8_t *in, uint8_t *out,
+    float *scale)
+{
+    PoolingParamSpec p;
+    memset(&p, 0, sizeof(p));
+    p.kernel_t = 1;
+    p.kernel_h = kh;
+    p.kernel_w = kw;
+    p.stride_t = 1;
+    p.stride_h = sh;
+    p.stride_w = sw;
+    p.pad_top = pt;
+    p.pad_bottom = pt;
+    p.pad_left = pl;
+    p.pad_right = pl;
+    p.round_mode = ROUND_CEIL;
+    p.mode = mode == 0 ? POOLING_MAX : POOLING_MEAN;
+    p.count_include_pad = count_include_pad != 0;
+    TensorDesc inDesc = tensor4df(DT_U8_Q, DF_NCHWC16, n, c, ih, iw);
+    TensorDesc outDesc = tensor4df(DT_U8_Q, DF_NCHWC16, n, c, oh, ow);
+    return (int)pooling_uint8(inDesc, in, p, outDesc, out, scale);
+}
 }  // extern "C"

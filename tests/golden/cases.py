@@ -193,3 +193,24 @@ def matmul_inputs(name):
     A, B = make(seed, a_shape, a_dt), make(seed + 1, b_shape, b_dt)
     bias = synth.normal(seed + 2, (bias_n,)) if bias_n else None
     return (A, a_dt, a_s, ta, B, b_dt, b_s, tb, bias, c_dt, c_s)
+
+
+# ---- u8 pooling ------------------------------------------------------------------------------------
+# (n, c, ih, iw, kernel, stride, pad, mean, count_include_pad, ceil)
+POOL_CASES = [(2, 32, 9, 9, 3, 2, 1, 0, 0, 0), (2, 32, 9, 9, 3, 2, 1, 1, 0, 0), (2, 32, 9, 9, 3, 2, 1, 1, 1, 0),
+              (1, 16, 7, 7, 7, 1, 0, 1, 0, 0), (1, 16, 7, 7, 7, 1, 0, 0, 0, 0), (2, 64, 14, 14, 2, 2, 0, 0, 0, 0),
+              (2, 64, 14, 14, 2, 2, 0, 1, 0, 0), (1, 16, 10, 13, 3, 1, 1, 1, 0, 0), (1, 48, 8, 8, 3, 2, 0, 0, 0, 1),
+              (1, 48, 8, 8, 3, 2, 0, 1, 1, 1), (1, 16, 5, 5, 5, 1, 2, 1, 0, 0), (1, 64, 56, 56, 3, 2, 1, 0, 0, 0)]
+
+
+def pool_out_hw(case):
+    n, c, ih, iw, k, s, p, mean, cip, ceil = case
+    if ceil:
+        return (ih + 2 * p - k + s - 1) // s + 1, (iw + 2 * p - k + s - 1) // s + 1
+    return (ih + 2 * p - k) // s + 1, (iw + 2 * p - k) // s + 1
+
+
+def pool_input(i):
+    n, c, ih, iw = POOL_CASES[i][:4]
+    # mean windows below the zero point store 255 in the reference: keep both kinds of windows in the data
+    return synth.u8(9100 + i, (n * c * ih * iw,))

@@ -153,7 +153,26 @@ def matmul_outputs():
     return out
 
 
+def pool_outputs():
+    """the reference's u8 pooling (cpu/x86/int8/avx512/pooling_int8.cpp)"""
+    import ctypes as C
+    O.ref.ref_pooling_u8.argtypes = [C.c_uint32] * 12 + [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
+    out = {}
+    for i, case in enumerate(cases.POOL_CASES):
+        n, c, ih, iw, k, s, p, mean, cip, ceil = case
+        oh, ow = cases.pool_out_hw(case)
+        x = cases.pool_input(i)
+        y = np.zeros(n * c * oh * ow, np.uint8)
+        sc = np.array([3.5, -1.0], np.float32)
+        rc = O.ref.ref_pooling_u8(n, c, ih, iw, oh, ow, k, k, s, s, p, p, mean, cip, ptr(x), ptr(y), ptr(sc))
+        assert rc == 0, case
+        out["p%d" % i] = y
+        out["p%d_scale" % i] = sc
+    return out
+
+
 def main():
+    np.savez_compressed(os.path.join(HERE, "pooling.npz"), **pool_outputs())
     np.savez_compressed(os.path.join(HERE, "matmul.npz"), **matmul_outputs())
     np.savez_compressed(os.path.join(HERE, "bnn.npz"), **bnn_outputs())
     np.savez_compressed(os.path.join(HERE, "gemv_row.npz"), **gemv_row_outputs())

@@ -281,3 +281,27 @@ def test_ref_matmul_sweep():
                 rc, Cr, sr = O.ref_matmul(*args)
                 Cp, sp = O.port_matmul(*args)
                 assert rc == 0 and Cr.tobytes() == Cp.tobytes() and np.float32(sr) == np.float32(sp), (m, k, n, ta, tb, c_dt)
+
+
+def _port_pool(i):
+    case = cases.POOL_CASES[i]
+    n, c, ih, iw, k, s, p, mean, cip, ceil = case
+    oh, ow = cases.pool_out_hw(case)
+    x = cases.pool_input(i)
+    y = np.zeros(n * c * oh * ow, np.uint8)
+    sc = np.array([3.5, -1.0], np.float32)
+    rc = O.port.oracle_pooling_u8(n, c, ih, iw, oh, ow, k, k, s, s, p, p, mean, cip, ptr(x), ptr(y), ptr(sc))
+    return rc, y, sc
+
+
+def test_golden_pooling():
+    g = np.load(os.path.join(GOLD, "pooling.npz"))
+    for i in range(len(cases.POOL_CASES)):
+        rc, y, sc = _port_pool(i)
+        assert rc == 0 and y.tobytes() == g["p%d" % i].tobytes() and sc.tobytes() == g["p%d_scale" % i].tobytes(), cases.POOL_CASES[i]
+    # a mean window whose values all lie below the zero point stores 255 (logical shift of a negative product)
+    x = np.full(16 * 4 * 4, 100, np.uint8)
+    y = np.zeros(16 * 2 * 2, np.uint8)
+    sc = np.array([1.0, 0.0], np.float32)
+    assert O.port.oracle_pooling_u8(1, 16, 4, 4, 2, 2, 2, 2, 2, 2, 0, 0, 1, 0, ptr(x), ptr(y), ptr(sc)) == 0
+    assert (y == 255).all()
