@@ -24,6 +24,71 @@ __device__ __forceinline__ uint32_t mean_byte(int32_t acc, int32_t pool)
     return v > 255u ? 255u : v;
 }
 
+// Windows of at most K x K taps (K = 2, 3): every tap is loaded before the first is used, so a thread has up
+// to nine 16-byte requests in flight; taps outside the clipped window repeat the first tap (maximum) or count
+// zero (mean).
+template <int K>
+__global__ void __launch_bounds__(256) pooling_u8_c16_small_kernel(const uint8_t *__restrict__ in, uint8_t *__restrict__ out, PoolGeom g)
+{
+    const uint64_t total = (uint64_t)g.planes * g.oh * g.ow;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t w = (uint32_t)(i % g.ow);
+        const uint64_t r = i / g.ow;
+        const uint32_t h = (uint32_t)(r % g.oh);
+        const uint64_t plane = r / g.oh;
+        int hs = (int)(h * g.sh) - (int)g.pt, ws = (int)(w * g.sw) - (int)g.pl;
+        const int he = min(hs + (int)g.kh, (int)g.ih), we = min(ws + (int)g.kw, (int)g.iw);
+        hs = max(hs, 0);
+        ws = max(ws, 0);
+        const uint4 *src = reinterpret_cast<const uint4 *>(in + plane * g.ih * g.iw * 16);
+        uint4 v[K * K];
+#pragma unroll
+        for (int dy = 0; dy < K; ++dy) {
+#pragma unroll
+            for (int dx = 0; dx < K; ++dx) {
+                const bool inside = hs + dy < he && ws + dx < we;
+                const int y = inside ? hs + dy : hs, x = inside ? ws + dx : ws;
+                v[dy * K + dx] = __ldg(src + (size_t)y * g.iw + x);
+                if (g.mean && !inside) {
+                    v[dy * K + dx] = make_uint4(0, 0, 0, 0);
+                }
+            }
+        }
+        uint4 res;
+        if (!g.mean) {
+            uint4 m = v[0];
+#pragma unroll
+            for (int t = 1; t < K * K; ++t) {
+                m.x = __vmaxu4(m.x, v[t].x);
+                m.y = __vmaxu4(m.y, v[t].y);
+                m.z = __vmaxu4(m.z, v[t].z);
+                m.w = __vmaxu4(m.w, v[t].w);
+            }
+            res = m;
+        } else {
+            const int n = (he - hs) * (we - ws);
+            const int32_t pool = g.count_include_pad ? g.factor : 65536 / n;
+            uint32_t q[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                int32_t acc[4] = {-128 * n, -128 * n, -128 * n, -128 * n};
+#pragma unroll
+                for (int t = 0; t < K * K; ++t) {
+                    const uint32_t word = k == 0 ? v[t].x : (k == 1 ? v[t].y : (k == 2 ? v[t].z : v[t].w));
+                    acc[0] += (int32_t)(word & 0xFFu);
+                    acc[1] += (int32_t)((word >> 8) & 0xFFu);
+                    acc[2] += (int32_t)((word >> 16) & 0xFFu);
+                    acc[3] += (int32_t)(word >> 24);
+                }
+                q[k] = mean_byte(acc[0], pool) | (mean_byte(acc[1], pool) << 8) | (mean_byte(acc[2], pool) << 16) |
+                    (mean_byte(acc[3], pool) << 24);
+            }
+            res = make_uint4(q[0], q[1], q[2], q[3]);
+        }
+        reinterpret_cast<uint4 *>(out)[i] = res;
+    }
+}
+
 __global__ void __launch_bounds__(256) pooling_u8_c16_kernel(const uint8_t *__restrict__ in, uint8_t *__restrict__ out, PoolGeom g)
 {
     const uint64_t total = (uint64_t)g.planes * g.oh * g.ow;
@@ -154,8 +219,14 @@ extern "C" EE pooling_cuda_b200(const TensorDesc *inputDesc, const void *input, 
         return NOT_MATCH;
     }
     const uint64_t blocks = (total + 255) / 256;
-    const uint32_t grid = (uint32_t)(blocks < (uint64_t)c->sm_count * 16 ? blocks : (uint64_t)c->sm_count * 16);
-    pooling_u8_c16_kernel<<<grid, 256, 0, tls().stream>>>(d_in, d_out, g);
+    const uint32_t grid = (uint32_t)(blocks < (uint64_t)c->sm_count * 32 ? blocks : (uint64_t)c->sm_count * 32);
+    if (g.kh <= 2 && g.kw <= 2) {
+        pooling_u8_c16_small_kernel<2><<<grid, 256, 0, tls().stream>>>(d_in, d_out, g);
+    } else if (g.kh <= 3 && g.kw <= 3) {
+        pooling_u8_c16_small_kernel<3><<<grid, 256, 0, tls().stream>>>(d_in, d_out, g);
+    } else {
+        pooling_u8_c16_kernel<<<grid, 256, 0, tls().stream>>>(d_in, d_out, g);
+    }
     count_launch();
     B200_CUDA(cudaGetLastError());
     return sg.finish();

@@ -321,14 +321,14 @@ def resnet_conv(peaks, batch=64, iters=5, out_u8=False, once=False):
 
 
 def pooling(peaks, iters=10):
-    """u8 pooling, NCHWc16: the 3x3 stride-2 maximum after a ResNet stem (64 x 112 x 112, batch 64: 51 MB in, 13 MB out)
-    and a 2x2 stride-2 mean on 256 x 56 x 56."""
+    """u8 pooling, NCHWc16: the 3x3 stride-2 maximum after a ResNet stem (64 x 112 x 112, batch 256: 206 MB in, 51 MB
+    out -- larger than L2) and a 2x2 stride-2 mean on 256 x 56 x 56."""
     from . import pooling as pool_call, pooling_param
     torch = _torch()
     L, tm = lib(), Timer()
     rows = []
-    for name, (n, c, hw, k, s, pad, mean) in (("max 3x3 s2 p1 64x112x112 b64", (64, 64, 112, 3, 2, 1, False)),
-                                              ("mean 2x2 s2 256x56x56 b64", (64, 256, 56, 2, 2, 0, True))):
+    for name, (n, c, hw, k, s, pad, mean) in (("max 3x3 s2 p1 64x112x112 b256", (256, 64, 112, 3, 2, 1, False)),
+                                              ("mean 2x2 s2 256x56x56 b256", (256, 256, 56, 2, 2, 0, True))):
         oh = (hw + 2 * pad - k) // s + 1
         x = torch.randint(128, 256, (n * c * hw * hw,), dtype=torch.uint8, device="cuda")
         y = torch.empty(n * c * oh * oh, dtype=torch.uint8, device="cuda")
