@@ -102,6 +102,10 @@ class PoolingParamSpec(C.Structure):
 POOLING_MAX, POOLING_MEAN = 0, 1
 
 
+class Scatter(C.Structure):
+    _fields_ = [("n_dest", C.c_uint32), ("dest", C.c_void_p * 8), ("ld", C.c_uint32), ("col0", C.c_uint32)]
+
+
 class ConvExt(C.Structure):
     """bolt_b200_conv_ext"""
     _fields_ = [("output_scale", C.c_float), ("filter_scales", C.c_void_p)]
@@ -124,6 +128,10 @@ SIGNATURES = {
     "bolt_b200_use_para": (C.c_int, [_vp]),
     "bolt_b200_i8_mma_rate": (C.c_int, [C.c_uint32, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "bolt_b200_selftest_wait_limit": (C.c_int, [C.c_uint32]),
+    "bolt_b200_gemm_u8s8_scatter": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, _vp, _vp, _vp, _vp, _vp]),
+    "bolt_b200_ipc_export": (C.c_int, [_vp, _vp]),
+    "bolt_b200_ipc_import": (C.c_int, [_vp, C.POINTER(C.c_void_p)]),
+    "bolt_b200_ipc_close": (C.c_int, [_vp]),
     "pooling_cuda_b200": (C.c_int, [_TDp, _vp, C.POINTER(PoolingParamSpec), _vp, _TDp, _vp]),
     "matmul_infer_output_size_cuda_b200": (C.c_int, [_TDp, C.c_int, _TDp, C.c_int, _TDp]),
     "matmul_infer_forward_tmp_bytes_cuda_b200": (C.c_int, [_TDp, C.c_int, _TDp, C.c_int, _TDp, C.c_float, C.POINTER(C.c_uint32)]),

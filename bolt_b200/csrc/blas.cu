@@ -160,6 +160,8 @@ EE run_gemm(U32 N, U32 M, U32 K, bool a_t, const void *A, const void *B, const v
     if (gemm_tcgen05_eligible(M, N, K, dA, dB, Kp, a_t)) {
         ret = launch_gemm_tcgen05(M, N, K, dA, dB, Kp, dC, ep, st);
         tls().last_gemm_tc = 1;
+    } else if (ep.scatter_n > 0) {
+        return NOT_SUPPORTED;  // the scatter epilogue exists on the tensor-core path only
     } else {
         ret = launch_gemm_simt(M, N, K, dA, a_t, dB, Kp, dC, ep, st);
         tls().last_gemm_tc = 0;
@@ -311,6 +313,43 @@ EE bolt_b200_gemm_u8s8_ex(U32 N, U32 M, U32 K, const void *A, const void *packed
         return NOT_SUPPORTED;
     }
     return run_gemm(N, M, K, false, A, packedB, offsetC, C, ep);
+}
+
+EE bolt_b200_gemm_u8s8_scatter(U32 N, U32 M, U32 K, const void *A, const void *packedB, const I32 *offsetC,
+    const bolt_b200_gemm_epilogue *e, const bolt_b200_scatter *sc)
+{
+    if (e == nullptr || sc == nullptr) {
+        return NULL_POINTER;
+    }
+    if (e->out_dt != DT_U8_Q || sc->n_dest == 0 || sc->n_dest > 8 || e->col_factor != nullptr) {
+        return NOT_SUPPORTED;
+    }
+    if (!is_device_ptr(A) || !is_device_ptr(packedB) || (offsetC != nullptr && !is_device_ptr(offsetC))) {
+        return NOT_MATCH;  // device memory only: the destinations are peers' buffers
+    }
+    GemmEpilogue ep;
+    std::memset(&ep, 0, sizeof(ep));
+    ep.out_kind = 2;
+    ep.num = e->out_scale;
+    ep.per_channel = 1;
+    ep.sA = e->sA;
+    ep.sB = e->sB;
+    ep.sA_dev = e->d_sA;
+    ep.row_scale = e->row_scale;
+    ep.col_scale = e->col_scale;
+    ep.prefetch = e->prefetch;
+    ep.prefetch_bytes = e->prefetch_bytes;
+    for (U32 q = 0; q < sc->n_dest; ++q) {
+        if (sc->dest[q] == nullptr) {
+            return NULL_POINTER;
+        }
+        ep.scatter_dst[q] = sc->dest[q];
+    }
+    ep.scatter_n = sc->n_dest;
+    ep.scatter_ld = sc->ld;
+    ep.scatter_col0 = sc->col0;
+    // C of the common path: the first destination (used only for the argument checks)
+    return run_gemm(N, M, K, false, A, packedB, offsetC, sc->dest[0], ep);
 }
 
 // =============================== GEMV ========================================================

@@ -65,6 +65,7 @@ struct DeviceCtx {
     int max_pairs = -1;  // co-resident 2-CTA clusters of the tensor-core GEMM (-1: not queried yet)
     int sm_count = 148;
     int *d_status = nullptr;      // device-side error word
+    void *d_scatter_maps = nullptr;  // 8 tensor maps of a scatter GEMM (allocated on first use)
     float *d_scratch = nullptr;   // small device scratch for reductions (absmax etc.)
     unsigned *d_scratch_u = nullptr;
     std::mutex mu;       // guards the staging workspace (one staged call at a time)
@@ -169,6 +170,9 @@ struct GemmEpilogue {
     const float *col_factor;   // [N] or null: ready-made per-column factors (then nothing is divided in the kernel)
     const void *prefetch;      // device memory a later call will read (the next layer's weight), or null:
     size_t prefetch_bytes;     // brought into L2 while this GEMM runs
+    // u8 output stored into scatter_n matrices [M][scatter_ld] (this GPU's and its peers') at column scatter_col0
+    void *scatter_dst[8];
+    uint32_t scatter_n, scatter_ld, scatter_col0;
 };
 
 // B: ALIGN(N,16) rows, pitch Kp = ALIGN(K,8) bytes, K contiguous, zero padded.

@@ -263,6 +263,47 @@ EE bolt_b200_use_para(const bolt_b200_para *para)
     return SUCCESS;
 }
 
+// ---- buffers shared between the processes of one box (one process per GPU) ----------------------------
+// export: a handle for a buffer obtained from bolt_b200_malloc; import: the peer's buffer as a pointer this
+// process may store to (peer access is enabled by the import); close: unmap it.
+EE bolt_b200_ipc_export(void *p, void *handle64)
+{
+    if (p == nullptr || handle64 == nullptr) {
+        return NULL_POINTER;
+    }
+    if (ctx() == nullptr) {
+        return UNKNOWN;
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    cudaIpcMemHandle_t h;
+    B200_CUDA(cudaIpcGetMemHandle(&h, p));
+    std::memcpy(handle64, &h, sizeof(h));
+    return SUCCESS;
+}
+
+EE bolt_b200_ipc_import(const void *handle64, void **p)
+{
+    if (p == nullptr || handle64 == nullptr) {
+        return NULL_POINTER;
+    }
+    if (ctx() == nullptr) {
+        return UNKNOWN;
+    }
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle64, sizeof(h));
+    B200_CUDA(cudaIpcOpenMemHandle(p, h, cudaIpcMemLazyEnablePeerAccess));
+    return SUCCESS;
+}
+
+EE bolt_b200_ipc_close(void *p)
+{
+    if (p == nullptr) {
+        return NULL_POINTER;
+    }
+    B200_CUDA(cudaIpcCloseMemHandle(p));
+    return SUCCESS;
+}
+
 EE bolt_b200_set_stream(void *cuda_stream)
 {
     tls().stream = reinterpret_cast<cudaStream_t>(cuda_stream);

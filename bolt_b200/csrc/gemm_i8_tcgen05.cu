@@ -78,6 +78,11 @@ struct Params {
     int *status;
     int vec_ok;             // rows of C are 16-byte aligned -> vector stores allowed
     uint32_t prefetch_slice;  // bytes of ep.prefetch each CTA asks for (0: none)
+    // scatter (u8 output through TMA stores only): every tile is stored into n_scatter destinations -- this GPU's
+    // and its peers' copies of a wider [M][ld] matrix -- at column scatter_col0 + n; the tensor maps lie in
+    // device memory
+    const CUtensorMap *scatter_maps;
+    uint32_t n_scatter, scatter_col0;
 };
 
 // Raster: groups of GROUP_M row blocks, inside a group the row block runs fastest.
@@ -745,7 +750,14 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                         __syncwarp();
                         if (lane == 0) {
                             // rows beyond M are clipped by the tensor map
-                            tma_store_2d(&map_c, stg, (int)(n0 + c * 32), (int)(m0 + quad * 32));
+                            if (p.n_scatter == 0) {
+                                tma_store_2d(&map_c, stg, (int)(n0 + c * 32), (int)(m0 + quad * 32));
+                            } else {
+                                // the same box to every destination (plain stores over NVLink for the peers')
+                                for (uint32_t q = 0; q < p.n_scatter; ++q) {
+                                    tma_store_2d(p.scatter_maps + q, stg, (int)(p.scatter_col0 + n0 + c * 32), (int)(m0 + quad * 32));
+                                }
+                            }
                         }
                     } else if (row_ok) {
                         uint8_t *out = reinterpret_cast<uint8_t *>(p.C) + (size_t)m * p.N + n0 + c * 32;
@@ -1089,6 +1101,36 @@ EE launch_gemm_tcgen05(uint32_t M, uint32_t N, uint32_t K, const uint8_t *A, con
         const uint32_t box[2] = {32, 32};
         const uint32_t estr[2] = {1, 1};
         tma_c = encode_tiled_u8(&map_c, 2, C, dims, strides, box, estr, 32);
+    }
+    p.scatter_maps = nullptr;
+    p.n_scatter = 0;
+    p.scatter_col0 = 0;
+    if (ep.scatter_n > 0) {
+        // one tensor map per destination over its [M][ld] matrix, kept in a small per-device array
+        if (!fast || ep.out_kind != 2 || ep.scatter_n > 8 || ep.scatter_ld % 16 != 0 || ep.scatter_col0 % 32 != 0 ||
+            ep.scatter_col0 + N > ep.scatter_ld) {
+            return NOT_SUPPORTED;
+        }
+        CUtensorMap maps[8];
+        for (uint32_t q = 0; q < ep.scatter_n; ++q) {
+            const uint64_t dims[2] = {ep.scatter_ld, M};
+            const uint64_t strides[1] = {ep.scatter_ld};
+            const uint32_t box[2] = {32, 32};
+            const uint32_t estr[2] = {1, 1};
+            if (ep.scatter_dst[q] == nullptr || (reinterpret_cast<uintptr_t>(ep.scatter_dst[q]) % 16) != 0 ||
+                !encode_tiled_u8(&maps[q], 2, ep.scatter_dst[q], dims, strides, box, estr, 32)) {
+                return NOT_SUPPORTED;
+            }
+        }
+        if (c->d_scatter_maps == nullptr) {
+            B200_CUDA(cudaMalloc(&c->d_scatter_maps, 8 * sizeof(CUtensorMap)));
+        }
+        // (the source is pageable host memory: the call returns once it has been staged)
+        B200_CUDA(cudaMemcpyAsync(c->d_scatter_maps, maps, ep.scatter_n * sizeof(CUtensorMap), cudaMemcpyHostToDevice, st));
+        p.scatter_maps = reinterpret_cast<const CUtensorMap *>(c->d_scatter_maps);
+        p.n_scatter = ep.scatter_n;
+        p.scatter_col0 = ep.scatter_col0;
+        tma_c = true;  // the scatter maps replace map_c
     }
     p.prefetch_slice = 0;
     if (ep.prefetch != nullptr && ep.prefetch_bytes >= 16 && (reinterpret_cast<uintptr_t>(ep.prefetch) % 16) == 0) {

@@ -290,6 +290,28 @@ EE bolt_b200_gemm_u8s8_ex(U32 N, U32 M, U32 K, const void *A, const void *packed
 /* factor[n] = num / (sA * sB[n]) in the reference's operation order (fp32 multiply, fp32 divide;
  * fully_connected.cpp:396,409): num = 1 for fp32 output, the output scale for u8 output.  d_sA (device
  * scalar) overrides sA, col_scale (device [N]) overrides sB.  factor: device [N]. */
+/* The same GEMM with a u8 result that is stored, tile by tile from the epilogue, into n_dest copies of a wider
+ * matrix [M][ld] at columns col0 .. col0 + N - 1: this GPU's copy and its peers' (pointers obtained with
+ * bolt_b200_ipc_import, or peer-enabled allocations of one process).  It is the N-split of a GEMM over the
+ * GPUs of one box with the all-gather fused into the kernel: every rank computes its N columns and leaves them
+ * in everybody's [M][ld] result over NVLink while it computes the next tile.  The caller synchronises the
+ * ranks afterwards (a barrier); until then other ranks' columns of a destination are not complete.
+ * Device pointers only; N % 32 == 0, ld % 16 == 0, col0 % 32 == 0, at most 8 destinations, K % 16 == 0.
+ * No counterpart in the reference (which is a single-process CPU library). */
+typedef struct {
+    U32 n_dest;
+    void *dest[8];
+    U32 ld;
+    U32 col0;
+} bolt_b200_scatter;
+EE bolt_b200_gemm_u8s8_scatter(U32 N, U32 M, U32 K, const void *A, const void *packedB, const I32 *offsetC,
+    const bolt_b200_gemm_epilogue *ep, const bolt_b200_scatter *sc);
+/* Buffers shared between the processes of one box: a 64-byte handle for memory from bolt_b200_malloc, the
+ * peer's mapping of it, and the unmapping. */
+EE bolt_b200_ipc_export(void *p, void *handle64);
+EE bolt_b200_ipc_import(const void *handle64, void **p);
+EE bolt_b200_ipc_close(void *p);
+
 EE bolt_b200_col_factor(F32 num, F32 sA, const F32 *d_sA, F32 sB, const F32 *col_scale, U32 N, F32 *factor);
 /* Extension: F32 -> U8_Q quantization with the scale read from device memory. */
 EE bolt_b200_quantize_f32_u8_dev(const F32 *data, uint64_t n, UINT8 *q, const F32 *d_scale);

@@ -387,3 +387,41 @@ def test_mvm_row_golden_and_sweep():
     assert not bad, bad[:10]
     Mx, v = synth.u8(1, (2048, 4096)), synth.s8(2, (4096,))
     assert same_bits(mvm_row_gpu(Mx, v, [-1, 0.0005]), O.port_gemv_row(Mx, v, [-1, 0.0005]))
+
+
+def test_gemm_scatter_into_wider_matrices():
+    """The scatter epilogue on one GPU: a [M, 256] product stored at column 128 of two [M, 512] matrices (the fused
+    all-gather of the N-split, with both destinations local).  The columns must equal the plain u8 GEMM, everything
+    else must stay as it was."""
+    import torch
+
+    m, k, n, ld, col0 = 300, 512, 256, 512, 128
+    A, W = synth.u8(61, (m, k)), synth.s8(62, (k, n))
+    bdesc = B.tensor2df(B.DT_I8, B.DF_NORMAL, k, n)
+    nbytes, rhs = B.matrix_matrix_multiply_transform_rhs_bytes(bdesc)
+    d_a, d_w, d_pack = to_dev(A), to_dev(W), dev_zeros(nbytes)
+    B.matrix_matrix_multiply_transform_rhs(bdesc, dptr(d_w), dptr(d_pack))
+    sB = (np.abs(synth.normal(63, (n,))) * 300 + 900).astype(np.float32)
+    rs = (np.abs(synth.normal(64, (m,))) * 10 + 30).astype(np.float32)
+    d_sb, d_rs = to_dev(sB), to_dev(rs)
+    ep = B.GemmEpilogue()
+    ep.out_dt, ep.accumulate, ep.out_scale, ep.sA, ep.sB = B.DT_U8_Q, 0, 40.0, 1.0, 1.0
+    ep.row_scale, ep.col_scale = dptr(d_rs), dptr(d_sb)
+    plain = dev_zeros(m * n)
+    B.CHECK_STATUS(B.lib().bolt_b200_gemm_u8s8_ex(n, m, k, dptr(d_a), dptr(d_pack), dptr(d_pack, rhs), dptr(plain), C.byref(ep)))
+    wide = [torch.full((m * ld,), 7, dtype=torch.uint8, device="cuda") for _ in range(2)]
+    sc = B.Scatter()
+    sc.n_dest, sc.ld, sc.col0 = 2, ld, col0
+    sc.dest[0], sc.dest[1] = wide[0].data_ptr(), wide[1].data_ptr()
+    B.CHECK_STATUS(B.lib().bolt_b200_gemm_u8s8_scatter(n, m, k, dptr(d_a), dptr(d_pack), dptr(d_pack, rhs), C.byref(ep), C.byref(sc)))
+    B.CHECK_STATUS(B.lib().bolt_b200_synchronize(), "synchronize")
+    assert B.lib().bolt_b200_last_gemm_used_tensor_cores() == 1
+    want = np.full((m, ld), 7, np.uint8)
+    want[:, col0:col0 + n] = to_host(plain, np.uint8, m * n).reshape(m, n)
+    for wd in wide:
+        assert np.array_equal(wd.cpu().numpy().reshape(m, ld), want)
+    # refused: a column offset that is not a multiple of 32, a destination count beyond 8
+    sc.col0 = 100
+    assert B.lib().bolt_b200_gemm_u8s8_scatter(n, m, k, dptr(d_a), dptr(d_pack), dptr(d_pack, rhs), C.byref(ep), C.byref(sc)) == B.NOT_SUPPORTED
+    sc.col0, sc.n_dest = col0, 9
+    assert B.lib().bolt_b200_gemm_u8s8_scatter(n, m, k, dptr(d_a), dptr(d_pack), dptr(d_pack, rhs), C.byref(ep), C.byref(sc)) == B.NOT_SUPPORTED
