@@ -211,3 +211,71 @@ class ShardedFFN:
     def assembled(self, M):
         """`[M, N]` from the shard-major gather buffer (after gather(M))"""
         return self.full[: self.world * M * self.nloc].view(self.world, M, self.nloc).permute(1, 0, 2).reshape(M, self.N)
+
+    # ---- the all-gather fused into the GEMM: every rank stores its tiles into all ranks' [M, N] results -------
+    def setup_fused(self):
+        """Allocates this rank's `[max_m, N]` result with the library's allocator, exchanges its handle with the other
+        ranks (one process per GPU) and maps theirs.  Needs an initialised process group."""
+        import torch.distributed as dist
+
+        from . import CHECK_STATUS
+
+        L = self.lib
+        L.bolt_b200_malloc.restype = C.c_void_p
+        self.result_ptr = L.bolt_b200_malloc(C.c_size_t(self.max_m * self.N))
+        if not self.result_ptr:
+            raise MemoryError("bolt_b200_malloc")
+        handle = (C.c_char * 64)()
+        CHECK_STATUS(L.bolt_b200_ipc_export(C.c_void_p(self.result_ptr), handle), "ipc_export")
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle.raw))
+        self.dest = []
+        self.imported = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.dest.append(self.result_ptr)
+                continue
+            p = C.c_void_p()
+            CHECK_STATUS(L.bolt_b200_ipc_import(C.c_char_p(h), C.byref(p)), "ipc_import")
+            self.dest.append(p.value)
+            self.imported.append(p.value)
+        self.flag = self.torch.zeros(1, dtype=self.torch.int32, device="cuda")
+        dist.barrier()
+
+    def fused(self, M):
+        """this rank's columns of `[M, N]` into every rank's result, then a one-element all-reduce as the barrier
+        after which all columns of the local result are complete"""
+        import torch.distributed as dist
+
+        from . import CHECK_STATUS, DT_U8_Q, GemmEpilogue, Scatter
+
+        ep = GemmEpilogue()
+        ep.out_dt, ep.accumulate, ep.out_scale, ep.sA, ep.sB = DT_U8_Q, 0, 40.0, 1.0, 1.0
+        ep.row_scale = C.c_void_p(self.rs.data_ptr())
+        ep.col_scale = C.c_void_p(self.sB.data_ptr())
+        sc = Scatter()
+        sc.n_dest, sc.ld, sc.col0 = self.world, self.N, self.rank * self.nloc
+        for r in range(self.world):
+            sc.dest[r] = self.dest[r]
+        CHECK_STATUS(self.lib.bolt_b200_gemm_u8s8_scatter(self.nloc, M, self.K, C.c_void_p(self.a.data_ptr()),
+                                                          C.c_void_p(self.packed.data_ptr()),
+                                                          C.c_void_p(self.packed.data_ptr() + self.rhs), C.byref(ep), C.byref(sc)),
+                     "gemm scatter")
+        dist.all_reduce(self.flag)
+
+    def fused_result(self, M):
+        """torch view of the first M rows of this rank's fused result"""
+        class _Raw:
+            pass
+
+        raw = _Raw()
+        raw.__cuda_array_interface__ = {"shape": (M, self.N), "typestr": "|u1", "data": (int(self.result_ptr), False), "version": 2}
+        return self.torch.as_tensor(raw, device="cuda")
+
+    def close_fused(self):
+        for p in getattr(self, "imported", []):
+            self.lib.bolt_b200_ipc_close(C.c_void_p(p))
+        self.imported = []
+        if getattr(self, "result_ptr", None):
+            self.lib.bolt_b200_free(C.c_void_p(self.result_ptr))
+            self.result_ptr = None
