@@ -2,6 +2,8 @@
 the byte-count and format entry points (pure host arithmetic) follow the reference's formulas."""
 import ctypes as C
 import os
+
+import pytest
 import re
 
 import bolt_b200 as B
@@ -149,3 +151,18 @@ def test_header_types_match_bolts_headers(tmp_path):
                  "DF_NKNxKx", "DF_NCHWC2NxC4", "DF_TRANSPOSE", "DF_NORMAL", "CONVOLUTION_ALGORITHM_POINTWISE",
                  "CONVOLUTION_ALGORITHM_DIRECT", "CONVOLUTION_ALGORITHM_BNN"):
         assert getattr(B, name) == int(vals[name]), name
+
+
+def test_matmul_output_size_is_host_arithmetic():
+    """matmul_infer_output_size_cpu (matmul.cpp:42-99): transposes, broadcast batch dimensions, rank alignment"""
+    F = B.DT_F32
+    cases_ = [(((2, 3, 40, 64), 0, (2, 3, 64, 24), 0), (2, 3, 40, 24)), (((2, 3, 64, 40), 1, (2, 3, 24, 64), 1), (2, 3, 40, 24)),
+              (((2, 3, 40, 64), 0, (1, 1, 64, 24), 0), (2, 3, 40, 24)), (((2, 3, 40, 64), 0, (64, 24), 0), (2, 3, 40, 24)),
+              (((1, 33, 50), 0, (5, 50, 17), 0), (5, 33, 17))]
+    for (a, ta, b, tb), want in cases_:
+        c = B.matmul_infer_output_size(B.tensor_nd(F, a), ta, B.tensor_nd(F, b), tb)
+        assert tuple(reversed(list(c.dims[: c.nDims]))) == want, (a, b)
+    with pytest.raises(B.BoltError):
+        B.matmul_infer_output_size(B.tensor_nd(F, (4, 8, 16)), 0, B.tensor_nd(F, (4, 17, 8)), 0)
+    with pytest.raises(B.BoltError):
+        B.matmul_infer_output_size(B.tensor_nd(F, (3, 8, 16)), 0, B.tensor_nd(F, (4, 16, 8)), 0)   # batch 3 against 4
