@@ -83,6 +83,9 @@ struct Params {
     // device memory
     const CUtensorMap *scatter_maps;
     uint32_t n_scatter, scatter_col0;
+    // 1: the four warps of a lane quadrant assemble [32 rows][128 B] boxes (half the tile's width) so that the peers
+    // receive 128-byte rows; needs 256-column tiles
+    uint32_t scatter_wide;
 };
 
 // Raster: groups of GROUP_M row blocks, inside a group the row block runs fastest.
@@ -613,13 +616,16 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             c_begin = min(units, grp * cpg);
             c_end = min(units, c_begin + cpg);
         };
-        auto fetch_raw = [&](uint32_t n_first, uint32_t cols, int32_t (&o)[NQ], float (&sb)[NQ]) {
+        constexpr bool wide = KIND == 4;  // scatter with 128-byte rows (its own instantiation: the common u8 path stays lean)
+        bool dead = false;  // wide scatter only: after a failed wait the warp still meets its quadrant's barriers
+        auto fetch_raw = [&](uint32_t tile_n0, uint32_t n_first, uint32_t cols, int32_t (&o)[NQ], float (&sb)[NQ]) {
 #pragma unroll
             for (int q = 0; q < NQ; ++q) {
                 o[q] = 0;
                 sb[q] = ep.sB;
                 const uint32_t j = lane + 32 * q;
-                const uint32_t n = n_first + j;
+                // wide scatter: slots 0-31 belong to chunk grp, slots 32-63 to chunk 4 + grp of the tile
+                const uint32_t n = wide ? tile_n0 + (((q == 0 ? grp : 4u + grp)) << 5) + lane : n_first + j;
                 if (j < cols && n < p.N) {
                     if (ep.offsetC != nullptr) {
                         asm volatile("ld.global.nc.b32 %0, [%1];" : "=r"(o[q]) : "l"(ep.offsetC + n));
@@ -677,7 +683,7 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             float sb[NQ];
             uint32_t cb, ce;
             my_chunks(t.units, cb, ce);
-            fetch_raw(t.n0 + cb * 32, (ce - cb) * 32, o, sb);
+            fetch_raw(t.n0, t.n0 + cb * 32, wide ? 64u : (ce - cb) * 32, o, sb);
             park(o, sb);
         }
         for (uint32_t it = 0; have; ++it) {
@@ -688,7 +694,10 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             uint32_t c_begin, c_end;
             my_chunks(t.units, c_begin, c_end);
             if (*reinterpret_cast<volatile uint32_t *>(&ctl->abort_flag) != 0) {
-                break;  // some role's bounded wait ran out
+                if (!wide) {
+                    break;  // some role's bounded wait ran out
+                }
+                dead = true;
             }
             const bool have_next = walk.next(p, t_next);
             int32_t o_next[NQ];
@@ -697,7 +706,7 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             if (new_cols) {
                 uint32_t cb, ce;
                 my_chunks(t_next.units, cb, ce);
-                fetch_raw(t_next.n0 + cb * 32, (ce - cb) * 32, o_next, sb_next);
+                fetch_raw(t_next.n0, t_next.n0 + cb * 32, wide ? 64u : (ce - cb) * 32, o_next, sb_next);
             }
             const uint32_t m = m0 + quad * 32 + lane;
             const bool row_ok = m < p.M;
@@ -705,18 +714,65 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             if (ROWS && row_ok) {
                 rs = ep.row_scale[m];
             }
-            bool ok = mbar_wait(&ctl->tmem_full[acc], acc_phase);
+            bool ok = dead ? true : mbar_wait(&ctl->tmem_full[acc], acc_phase);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
                 if (lane == 0) {
                     atomicExch(p.status, 3);
                     atomicExch(&ctl->abort_flag, 1u);
                 }
-                break;
+                if (!wide) {
+                    break;
+                }
+                dead = true;
             }
             tcgen05_fence_after();
             const uint32_t tbase = tmem_base + ((quad * 32u) << 16) + acc * MAX_BLOCK_N;
-            if (c_begin >= c_end) {
+            if (wide) {
+                // Scatter with 128-byte rows: in pass 0 the warps of this lane quadrant convert chunks 0-3 (chunk
+                // = column group), in pass 1 chunks 4-7; each pass fills the quadrant's [32 rows][128 B] box
+                // (128-byte swizzle) and one thread stores it to every destination.
+                uint8_t *box = smem_staging + quad * 4096;
+                const uint32_t bar_id = 1 + quad;
+                uint32_t ra[32], w[8];
+#pragma unroll 1
+                for (uint32_t pass = 0; pass < 2; ++pass) {
+                    if (!dead) {
+                        const uint32_t c = pass * 4 + grp;
+                        const uint32_t cl = pass * 32;
+                        tmem_ld32(tbase + c * 32, ra);
+                        tmem_ld_wait(ra);
+                        const uint32_t seen = chunk_to_u8_quick<ROWS>(offs, colf, cl, ep.num, rs, ra, w);
+                        if (__any_sync(0xffffffffu, seen > 255u)) {
+                            const Words8 e = chunk_to_u8_exact<ROWS>(tbase + c * 32, offs, colf, cl, ep.num, rs);
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) {
+                                w[q] = e.w[q];
+                            }
+                        }
+                        if (pass == 1) {
+                            release(acc);
+                        }
+                        if (grp == 0 && lane == 0) {
+                            tma_store_wait_read();  // the stores of the previous box have read it
+                        }
+                    }
+                    asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+                    if (!dead) {
+                        uint8_t *row = box + lane * 128;
+                        const uint32_t sw = lane & 7;
+                        *reinterpret_cast<uint4 *>(row + (((2 * grp) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                        *reinterpret_cast<uint4 *>(row + (((2 * grp + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+                        fence_proxy_async_smem();
+                    }
+                    asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+                    if (!dead && grp == 0 && lane == 0) {
+                        for (uint32_t q = 0; q < p.n_scatter; ++q) {
+                            tma_store_2d(p.scatter_maps + q, box, (int)(p.scatter_col0 + n0 + pass * 128), (int)(m0 + quad * 32));
+                        }
+                    }
+                }
+            } else if (c_begin >= c_end) {
                 release(acc);  // no columns of this tile: only the hand-back
             } else if (KIND >= 2) {
                 // u8 output, one 32-column chunk at a time (at most two per warp; the other warps of the scheduler
@@ -797,7 +853,7 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             t = t_next;
             have = have_next;
         }
-        if (KIND == 3 && lane == 0) {
+        if (KIND >= 3 && lane == 0) {
             // the staging buffer must have been read before the CTA's shared memory goes away; the
             // stores themselves complete before the grid does
             tma_store_wait_read();
@@ -998,6 +1054,8 @@ cudaError_t launch_kind(int kind, bool rows, uint32_t grid, cudaStream_t st, con
             return rows ? launch_one<1, true, F, PAIR>(grid, st, ma, mb, mc, p) : launch_one<1, false, F, PAIR>(grid, st, ma, mb, mc, p);
         case 2:
             return rows ? launch_one<2, true, F, PAIR>(grid, st, ma, mb, mc, p) : launch_one<2, false, F, PAIR>(grid, st, ma, mb, mc, p);
+        case 4:
+            return rows ? launch_one<4, true, F, PAIR>(grid, st, ma, mb, mc, p) : launch_one<4, false, F, PAIR>(grid, st, ma, mb, mc, p);
         default:
             return rows ? launch_one<3, true, F, PAIR>(grid, st, ma, mb, mc, p) : launch_one<3, false, F, PAIR>(grid, st, ma, mb, mc, p);
     }
@@ -1048,7 +1106,9 @@ EE launch_gemm_tcgen05(uint32_t M, uint32_t N, uint32_t K, const uint8_t *A, con
             (const void *)gemm_u8s8_tcgen05_kernel<0, false, F, true>, (const void *)gemm_u8s8_tcgen05_kernel<1, false, F, true>,
             (const void *)gemm_u8s8_tcgen05_kernel<2, false, F, true>, (const void *)gemm_u8s8_tcgen05_kernel<3, false, F, true>,
             (const void *)gemm_u8s8_tcgen05_kernel<1, true, F, true>, (const void *)gemm_u8s8_tcgen05_kernel<2, true, F, true>,
-            (const void *)gemm_u8s8_tcgen05_kernel<3, true, F, true>};
+            (const void *)gemm_u8s8_tcgen05_kernel<3, true, F, true>,
+            (const void *)gemm_u8s8_tcgen05_kernel<4, false, F, false>, (const void *)gemm_u8s8_tcgen05_kernel<4, true, F, false>,
+            (const void *)gemm_u8s8_tcgen05_kernel<4, false, F, true>, (const void *)gemm_u8s8_tcgen05_kernel<4, true, F, true>};
         B200_EE(raise_smem_limit(c, KF_GEMM, kernels, (int)(sizeof(kernels) / sizeof(kernels[0])), SMEM_BYTES));
     }
 
@@ -1076,6 +1136,15 @@ EE launch_gemm_tcgen05(uint32_t M, uint32_t N, uint32_t K, const uint8_t *A, con
     const uint32_t block_m = pair ? 2 * BLOCK_M : BLOCK_M;
     p.tiles_m = (M + block_m - 1) / block_m;
     p.block_n = pick_block_n(p.tiles_m, N, pair ? pairs : c->sm_count);
+    // scatter with 128-byte rows needs whole 256-column tiles
+    static const bool no_wide = [] {
+        const char *e = getenv("BOLT_B200_NO_WIDE_SCATTER");
+        return e != nullptr && e[0] != '\0' && e[0] != '0';
+    }();
+    const bool wide_scatter = ep.scatter_n > 0 && fast && ep.out_kind == 2 && N % 256 == 0 && !no_wide;
+    if (wide_scatter) {
+        p.block_n = 256;
+    }
     const uint32_t b_rows = pair ? p.block_n / 2 : p.block_n;
     p.stages = (uint32_t)(SMEM_RING_BYTES / (SMEM_A_STAGE + B200_ALIGN((size_t)b_rows * BLOCK_K, 1024)));
     if (p.stages > (uint32_t)MAX_STAGES) {
@@ -1105,6 +1174,7 @@ EE launch_gemm_tcgen05(uint32_t M, uint32_t N, uint32_t K, const uint8_t *A, con
     p.scatter_maps = nullptr;
     p.n_scatter = 0;
     p.scatter_col0 = 0;
+    p.scatter_wide = 0;
     if (ep.scatter_n > 0) {
         // one tensor map per destination over its [M][ld] matrix, kept in a small per-device array
         if (!fast || ep.out_kind != 2 || ep.scatter_n > 8 || ep.scatter_ld % 16 != 0 || ep.scatter_col0 % 32 != 0 ||
@@ -1115,10 +1185,10 @@ EE launch_gemm_tcgen05(uint32_t M, uint32_t N, uint32_t K, const uint8_t *A, con
         for (uint32_t q = 0; q < ep.scatter_n; ++q) {
             const uint64_t dims[2] = {ep.scatter_ld, M};
             const uint64_t strides[1] = {ep.scatter_ld};
-            const uint32_t box[2] = {32, 32};
+            const uint32_t box[2] = {wide_scatter ? 128u : 32u, 32};
             const uint32_t estr[2] = {1, 1};
             if (ep.scatter_dst[q] == nullptr || (reinterpret_cast<uintptr_t>(ep.scatter_dst[q]) % 16) != 0 ||
-                !encode_tiled_u8(&maps[q], 2, ep.scatter_dst[q], dims, strides, box, estr, 32)) {
+                !encode_tiled_u8(&maps[q], 2, ep.scatter_dst[q], dims, strides, box, estr, wide_scatter ? 128 : 32)) {
                 return NOT_SUPPORTED;
             }
         }
@@ -1130,6 +1200,7 @@ EE launch_gemm_tcgen05(uint32_t M, uint32_t N, uint32_t K, const uint8_t *A, con
         p.scatter_maps = reinterpret_cast<const CUtensorMap *>(c->d_scatter_maps);
         p.n_scatter = ep.scatter_n;
         p.scatter_col0 = ep.scatter_col0;
+        p.scatter_wide = wide_scatter ? 1u : 0u;
         tma_c = true;  // the scatter maps replace map_c
     }
     p.prefetch_slice = 0;
@@ -1143,7 +1214,7 @@ EE launch_gemm_tcgen05(uint32_t M, uint32_t N, uint32_t K, const uint8_t *A, con
     if (!fast) {
         e = launch_one<-1, false, EPI_WARPS_GENERAL, false>(grid, st, map_a, map_b, map_c, p);
     } else {
-        const int kind = ep.out_kind == 2 ? (tma_c ? 3 : 2) : ep.out_kind;
+        const int kind = ep.out_kind == 2 ? (p.scatter_wide ? 4 : (tma_c ? 3 : 2)) : ep.out_kind;
         e = pair ? launch_kind<true>(kind, rows, grid, st, map_a, map_b, map_c, p)
                  : launch_kind<false>(kind, rows, grid, st, map_a, map_b, map_c, p);
     }

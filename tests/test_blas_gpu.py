@@ -389,13 +389,15 @@ def test_mvm_row_golden_and_sweep():
     assert same_bits(mvm_row_gpu(Mx, v, [-1, 0.0005]), O.port_gemv_row(Mx, v, [-1, 0.0005]))
 
 
-def test_gemm_scatter_into_wider_matrices():
-    """The scatter epilogue on one GPU: a [M, 256] product stored at column 128 of two [M, 512] matrices (the fused
+@pytest.mark.parametrize("n,per_token", [(256, True), (512, True), (768, False), (288, True), (96, False)])
+def test_gemm_scatter_into_wider_matrices(n, per_token):
+    """The scatter epilogue on one GPU: a [M, n] product stored at column 128 of two [M, 1024] matrices (the fused
     all-gather of the N-split, with both destinations local).  The columns must equal the plain u8 GEMM, everything
-    else must stay as it was."""
+    else must stay as it was.  n a multiple of 256: boxes of 128-byte rows assembled by the four warps of a lane
+    quadrant; other n: one 32-byte-row box per warp."""
     import torch
 
-    m, k, n, ld, col0 = 300, 512, 256, 512, 128
+    m, k, ld, col0 = 300, 512, 1024, 128
     A, W = synth.u8(61, (m, k)), synth.s8(62, (k, n))
     bdesc = B.tensor2df(B.DT_I8, B.DF_NORMAL, k, n)
     nbytes, rhs = B.matrix_matrix_multiply_transform_rhs_bytes(bdesc)
@@ -405,19 +407,21 @@ def test_gemm_scatter_into_wider_matrices():
     rs = (np.abs(synth.normal(64, (m,))) * 10 + 30).astype(np.float32)
     d_sb, d_rs = to_dev(sB), to_dev(rs)
     ep = B.GemmEpilogue()
-    ep.out_dt, ep.accumulate, ep.out_scale, ep.sA, ep.sB = B.DT_U8_Q, 0, 40.0, 1.0, 1.0
-    ep.row_scale, ep.col_scale = dptr(d_rs), dptr(d_sb)
+    ep.out_dt, ep.accumulate, ep.out_scale, ep.sA, ep.sB = B.DT_U8_Q, 0, 40.0, 35.0, 1.0
+    ep.row_scale, ep.col_scale = (dptr(d_rs) if per_token else None), dptr(d_sb)
     plain = dev_zeros(m * n)
     B.CHECK_STATUS(B.lib().bolt_b200_gemm_u8s8_ex(n, m, k, dptr(d_a), dptr(d_pack), dptr(d_pack, rhs), dptr(plain), C.byref(ep)))
     wide = [torch.full((m * ld,), 7, dtype=torch.uint8, device="cuda") for _ in range(2)]
     sc = B.Scatter()
     sc.n_dest, sc.ld, sc.col0 = 2, ld, col0
     sc.dest[0], sc.dest[1] = wide[0].data_ptr(), wide[1].data_ptr()
-    B.CHECK_STATUS(B.lib().bolt_b200_gemm_u8s8_scatter(n, m, k, dptr(d_a), dptr(d_pack), dptr(d_pack, rhs), C.byref(ep), C.byref(sc)))
+    for _ in range(2):   # twice: the staging boxes are reused across launches
+        B.CHECK_STATUS(B.lib().bolt_b200_gemm_u8s8_scatter(n, m, k, dptr(d_a), dptr(d_pack), dptr(d_pack, rhs), C.byref(ep), C.byref(sc)))
     B.CHECK_STATUS(B.lib().bolt_b200_synchronize(), "synchronize")
     assert B.lib().bolt_b200_last_gemm_used_tensor_cores() == 1
     want = np.full((m, ld), 7, np.uint8)
     want[:, col0:col0 + n] = to_host(plain, np.uint8, m * n).reshape(m, n)
+    assert len(np.unique(want[:, col0:col0 + n])) > 50      # a result with content, not a saturated one
     for wd in wide:
         assert np.array_equal(wd.cpu().numpy().reshape(m, ld), want)
     # refused: a column offset that is not a multiple of 32, a destination count beyond 8
@@ -425,3 +429,31 @@ def test_gemm_scatter_into_wider_matrices():
     assert B.lib().bolt_b200_gemm_u8s8_scatter(n, m, k, dptr(d_a), dptr(d_pack), dptr(d_pack, rhs), C.byref(ep), C.byref(sc)) == B.NOT_SUPPORTED
     sc.col0, sc.n_dest = col0, 9
     assert B.lib().bolt_b200_gemm_u8s8_scatter(n, m, k, dptr(d_a), dptr(d_pack), dptr(d_pack, rhs), C.byref(ep), C.byref(sc)) == B.NOT_SUPPORTED
+
+
+def test_gemm_scatter_long_k_pairs():
+    """K = 4096 and M = 512: the CTA-pair kernel with the 128-byte-row scatter"""
+    import torch
+
+    m, k, n, ld, col0 = 512, 4096, 512, 1024, 512
+    A, W = synth.u8(71, (m, k)), synth.s8(72, (k, n))
+    bdesc = B.tensor2df(B.DT_I8, B.DF_NORMAL, k, n)
+    nbytes, rhs = B.matrix_matrix_multiply_transform_rhs_bytes(bdesc)
+    d_a, d_w, d_pack = to_dev(A), to_dev(W), dev_zeros(nbytes)
+    B.matrix_matrix_multiply_transform_rhs(bdesc, dptr(d_w), dptr(d_pack))
+    sB = (np.abs(synth.normal(73, (n,))) * 300 + 900).astype(np.float32)
+    d_sb = to_dev(sB)
+    ep = B.GemmEpilogue()
+    ep.out_dt, ep.accumulate, ep.out_scale, ep.sA, ep.sB = B.DT_U8_Q, 0, 40.0, 100.0, 1.0
+    ep.row_scale, ep.col_scale = None, dptr(d_sb)
+    plain = dev_zeros(m * n)
+    B.CHECK_STATUS(B.lib().bolt_b200_gemm_u8s8_ex(n, m, k, dptr(d_a), dptr(d_pack), dptr(d_pack, rhs), dptr(plain), C.byref(ep)))
+    wide = torch.full((m * ld,), 9, dtype=torch.uint8, device="cuda")
+    sc = B.Scatter()
+    sc.n_dest, sc.ld, sc.col0 = 1, ld, col0
+    sc.dest[0] = wide.data_ptr()
+    B.CHECK_STATUS(B.lib().bolt_b200_gemm_u8s8_scatter(n, m, k, dptr(d_a), dptr(d_pack), dptr(d_pack, rhs), C.byref(ep), C.byref(sc)))
+    B.CHECK_STATUS(B.lib().bolt_b200_synchronize(), "synchronize")
+    want = np.full((m, ld), 9, np.uint8)
+    want[:, col0:col0 + n] = to_host(plain, np.uint8, m * n).reshape(m, n)
+    assert np.array_equal(wide.cpu().numpy().reshape(m, ld), want)
