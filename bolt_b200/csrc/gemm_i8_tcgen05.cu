@@ -710,7 +710,9 @@ gemm_u8s8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             }
             const uint32_t m = m0 + quad * 32 + lane;
             const bool row_ok = m < p.M;
-            float rs = 0.f;
+            // rows beyond M get a harmless scale: a zero would turn their factors into infinities and send every
+            // chunk of a partly filled row block through the exact conversion (their bytes are never stored)
+            float rs = 1.f;
             if (ROWS && row_ok) {
                 rs = ep.row_scale[m];
             }
