@@ -202,7 +202,19 @@ def run_sharded_record(rank, world, lib, dist, stream, evict):
 
     K, N = 8192, 28672
     ffn = ShardedFFN(rank, world, K, N)
-    ffn.setup_fused()
+    # the fused variant needs buffers shared between the processes; every rank tries the set-up and one call, and
+    # the ranks agree on the outcome, so that a rank on which it is unavailable cannot leave the others waiting
+    fused_note = None
+    try:
+        ffn.setup_fused()
+        ffn.fused_compute(128)
+        torch.cuda.synchronize()
+        mine = 1
+    except Exception as exc:   # noqa: BLE001 -- reported in the record
+        mine, fused_note = 0, "%s: %s" % (type(exc).__name__, exc)
+    agreed = torch.tensor([mine], device="cuda")
+    dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+    fused_on = bool(agreed.item() == 1)
     one = None
     if rank == 0:
         # the unsplit problem on one GPU: all shards side by side
@@ -236,7 +248,7 @@ def run_sharded_record(rank, world, lib, dist, stream, evict):
         ms_g = timed(lambda: ffn.gather(M))
         ms_o = timed(lambda: ffn.overlapped(M)) if M >= 2048 else None
         # the gather fused into the GEMM's epilogue (peer stores) + a one-element all-reduce as the barrier
-        ms_f = timed(lambda: ffn.fused(M)) if M >= 128 else None
+        ms_f = timed(lambda: ffn.fused(M)) if (M >= 128 and fused_on) else None
         ops = 2.0 * M * N * K
         gathered = (world - 1) / world * M * N            # bytes every rank receives
         row = {"M": M, "compute_ms": ms_c, "gather_ms": ms_g, "overlapped_ms": ms_o,
@@ -284,7 +296,7 @@ def run_sharded_record(rank, world, lib, dist, stream, evict):
                 ref.copy_(one.block[: M * N])
             dist.broadcast(ref, 0)
             same = torch.equal(ffn.assembled(M).reshape(-1), ref)
-            if M >= 128:
+            if M >= 128 and fused_on:
                 ffn.fused(M)
                 torch.cuda.synchronize()
                 same = same and torch.equal(ffn.fused_result(M).reshape(-1), ref)
@@ -296,7 +308,10 @@ def run_sharded_record(rank, world, lib, dist, stream, evict):
     torch.cuda.synchronize()
     dist.barrier()
     ffn.close_fused()
-    return {"workload": "ffn N-split: K=8192 N=28672 u8 out, per-channel / per-token scales, M=1 through the GEMV kernel",
+    if not fused_on and fused_note is None:
+        fused_note = "unavailable on another rank"
+    return {"fused_available": fused_on, "fused_note": fused_note,
+            "workload": "ffn N-split: K=8192 N=28672 u8 out, per-channel / per-token scales, M=1 through the GEMV kernel",
             "world": world, "columns_per_gpu": N // world, "rows": rows,
             "mode": "gather = one all_gather_into_tensor of [M, N/world] u8 blocks into a shard-major buffer; "
                     "overlapped = 4 row chunks, gather of chunk i on a side stream while chunk i+1 computes; "

@@ -222,13 +222,17 @@ class ShardedFFN:
 
         L = self.lib
         L.bolt_b200_malloc.restype = C.c_void_p
+        # local, fallible part first; the exchange below is reached by every rank whatever happened here
+        mine = None
         self.result_ptr = L.bolt_b200_malloc(C.c_size_t(self.max_m * self.N))
-        if not self.result_ptr:
-            raise MemoryError("bolt_b200_malloc")
-        handle = (C.c_char * 64)()
-        CHECK_STATUS(L.bolt_b200_ipc_export(C.c_void_p(self.result_ptr), handle), "ipc_export")
+        if self.result_ptr:
+            handle = (C.c_char * 64)()
+            if L.bolt_b200_ipc_export(C.c_void_p(self.result_ptr), handle) == 0:
+                mine = bytes(handle.raw)
         handles = [None] * self.world
-        dist.all_gather_object(handles, bytes(handle.raw))
+        dist.all_gather_object(handles, mine)
+        if any(h is None for h in handles):
+            raise RuntimeError("a rank could not allocate or export its result buffer")
         self.dest = []
         self.imported = []
         for r, h in enumerate(handles):
@@ -240,13 +244,17 @@ class ShardedFFN:
             self.dest.append(p.value)
             self.imported.append(p.value)
         self.flag = self.torch.zeros(1, dtype=self.torch.int32, device="cuda")
-        dist.barrier()
 
     def fused(self, M):
         """this rank's columns of `[M, N]` into every rank's result, then a one-element all-reduce as the barrier
         after which all columns of the local result are complete"""
         import torch.distributed as dist
 
+        self.fused_compute(M)
+        dist.all_reduce(self.flag)
+
+    def fused_compute(self, M):
+        """the scatter GEMM alone (no collective)"""
         from . import CHECK_STATUS, DT_U8_Q, GemmEpilogue, Scatter
 
         ep = GemmEpilogue()
@@ -261,7 +269,6 @@ class ShardedFFN:
                                                           C.c_void_p(self.packed.data_ptr()),
                                                           C.c_void_p(self.packed.data_ptr() + self.rhs), C.byref(ep), C.byref(sc)),
                      "gemm scatter")
-        dist.all_reduce(self.flag)
 
     def fused_result(self, M):
         """torch view of the first M rows of this rank's fused result"""
