@@ -66,3 +66,23 @@ def test_gather_columns_two_gloo_ranks(tmp_path):
         procs.append(subprocess.Popen([sys.executable, str(script), ROOT], env=env))
     codes = [p.wait(timeout=180) for p in procs]
     assert codes == [0, 0]
+
+
+def test_scatter_offsets_agree_with_the_shard_ranges():
+    """The fused N-split stores rank r's columns at r * (N / world) of every rank's [M, N] result; that has to be the
+    same partition the gather-based path uses (shard_range), for the widths both paths accept."""
+    from bolt_b200.sharded import shard_range, shard_width
+
+    for N in (28672, 3072, 8192):
+        for world in (1, 2, 4, 8):
+            if N % (32 * world):
+                continue
+            nloc = N // world
+            assert shard_width(N, world) == nloc
+            covered = 0
+            for r in range(world):
+                n0, n1 = shard_range(N, world, r)
+                assert (n0, n1) == (r * nloc, (r + 1) * nloc)
+                assert n0 % 32 == 0            # the scatter epilogue's column offset rule
+                covered += n1 - n0
+            assert covered == N
